@@ -1,0 +1,326 @@
+"""Host-side planning for the multi-tensor step: descriptor tables, tile lists, workspace.
+
+The optimizer classes describe every tensor on the learned-optimizer path with
+a :class:`LoTensor`; :class:`LoPlan` turns the list into the device-resident
+tables the C ABI works on (include/pylo_b200.h) and issues the fixed launch
+sequence of one step.  Nothing here touches tensor values on the host.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib as L
+
+
+def _prod(xs) -> int:
+    out = 1
+    for x in xs:
+        out *= int(x)
+    return out
+
+
+@dataclass
+class LoTensor:
+    """One tensor on the learned-optimizer path (all tensors fp32, contiguous, on one CUDA device)."""
+
+    p: torch.Tensor
+    m: torch.Tensor                     # (3,) + shape
+    v: torch.Tensor                     # shape or (1,) + shape
+    fac_r: Optional[torch.Tensor]       # [3] + shape[dr -> 1]; fewer than 2 dims: (3,) + shape
+    fac_c: Optional[torch.Tensor]       # [3] + shape[dc -> 1]; fewer than 2 dims: (3,) + shape or None
+    fdims: Optional[Tuple[int, int]]    # (dc, dr) or None for fewer than 2 dims
+    rcm_axis: int = 0                   # axis of fac_r over which row_col_mean is taken
+    lr: float = 1e-3
+    wd: float = 0.0
+    clip_norm: float = 0.0
+    exp_mult: float = 0.0
+    step_mult: float = 1.0
+    out: Optional[torch.Tensor] = None  # CELO2 raw step
+    w: Optional[torch.Tensor] = None    # network weights in family layout
+    lr_mult: Optional[torch.Tensor] = None
+    slice_last2: bool = False           # normalise features per matrix (last two axes) instead of per tensor
+
+
+def geometry(shape: Sequence[int], fdims):
+    """(O, X, M, Y, I, r_is_a) of a contiguous tensor whose factored axes are fdims = (dc, dr)."""
+    dc, dr = fdims
+    ax, ay = (dc, dr) if dc < dr else (dr, dc)
+    O = _prod(shape[:ax])
+    X = int(shape[ax])
+    M = _prod(shape[ax + 1:ay])
+    Y = int(shape[ay])
+    I = _prod(shape[ay + 1:])
+    return O, X, M, Y, I, int(dr == ay)
+
+
+def _aligned16(*tensors) -> bool:
+    return all(t is None or t.data_ptr() % 16 == 0 for t in tensors)
+
+
+def make_tiles(sizes: Sequence[int]) -> Tuple[np.ndarray, List[Tuple[int, int]]]:
+    """Element-wise tiles over items of the given sizes; returns (tiles, [(tile0, n_tiles)] per item)."""
+    ranges, total = [], 0
+    for n in sizes:
+        k = (int(n) + L.TILE_ELEMS - 1) // L.TILE_ELEMS
+        ranges.append((total, k))
+        total += k
+    tiles = np.zeros(total, dtype=L.TILE_DTYPE)
+    for i, (t0, k) in enumerate(ranges):
+        tiles["tensor"][t0:t0 + k] = i
+        tiles["start"][t0:t0 + k] = np.arange(k, dtype=np.int64) * L.TILE_ELEMS
+    return tiles, ranges
+
+
+class DeviceTable:
+    """A numpy structured array mirrored in device memory through two pinned staging buffers."""
+
+    def __init__(self, host: np.ndarray, device):
+        self.host = host
+        self.nbytes = max(host.nbytes, 16)
+        self.dev = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self._stage = [torch.empty(self.nbytes, dtype=torch.uint8).pin_memory() for _ in range(2)]
+        self._events = [None, None]
+        self._turn = 0
+        self.upload()
+
+    @property
+    def ptr(self) -> int:
+        return self.dev.data_ptr()
+
+    def upload(self):
+        i = self._turn
+        self._turn ^= 1
+        if self._events[i] is not None:
+            self._events[i].synchronize()
+        if self.host.nbytes:
+            self._stage[i].numpy()[: self.host.nbytes] = self.host.view(np.uint8).reshape(-1)
+        self.dev.copy_(self._stage[i], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._events[i] = ev
+
+
+class LoPlan:
+    """Descriptor tables, tile lists and workspace for the tensors of one optimizer instance.
+
+    Two tables: one descriptor per tensor (phases A and A2 work on whole tensors) and one per
+    unit of element-wise work (phases B to C).  A unit is a tensor, or one matrix slice of a
+    tensor flagged ``slice_last2``; when nothing is sliced the two tables are one.
+    """
+
+    H = {L.FAM_ADAFAC: 32, L.FAM_CELO2: 8, L.FAM_VELO: 4}
+
+    def __init__(self, family: int, tensors: List[LoTensor], device):
+        self.family = family
+        self.tensors = tensors
+        self.device = torch.device(device)
+        T = len(tensors)
+        H = self.H[family]
+        tdesc = np.zeros(T, dtype=L.DESC_DTYPE)
+        ws_items = []  # (table, row, field, count)
+        atiles, generic = [], []
+        for i, t in enumerate(tensors):
+            shape = tuple(t.p.shape)
+            n = t.p.numel()
+            if n == 0:
+                raise ValueError("empty parameter tensors are not supported on the learned-optimizer path")
+            for name in ("p", "m", "v", "fac_r", "fac_c", "out"):
+                x = getattr(t, name)
+                if x is not None and not (x.is_cuda and x.dtype == torch.float32 and x.is_contiguous()):
+                    raise ValueError(f"{name} of tensor {i} must be a contiguous fp32 CUDA tensor")
+            d = tdesc[i]
+            d["n"], d["m_stride"], d["idx0"] = n, n, 0
+            d["lr"], d["wd"], d["clip_norm"] = t.lr, t.wd, t.clip_norm
+            d["exp_mult"], d["step_mult"] = t.exp_mult, t.step_mult
+            d["p"], d["m"], d["v"] = t.p.data_ptr(), t.m.data_ptr(), t.v.data_ptr()
+            d["out"] = t.out.data_ptr() if t.out is not None else 0
+            d["w"] = t.w.data_ptr() if t.w is not None else 0
+            d["lr_mult"] = t.lr_mult.data_ptr() if t.lr_mult is not None else 0
+            if t.fdims is None:
+                d["mode"] = L.MODE_VEC1D
+                d["O"] = d["X"] = d["M"] = d["I"] = 1
+                d["Y"] = min(n, 2**31 - 1)
+                d["r_is_a"] = 1
+                d["fac_a"] = t.fac_r.data_ptr()
+                d["fac_b"] = t.fac_c.data_ptr() if t.fac_c is not None else 0
+                d["rcm_pre"] = d["rcm_A"] = d["rcm_post"] = 1
+            else:
+                O, X, M, Y, I, r_is_a = geometry(shape, t.fdims)
+                d["O"], d["X"], d["M"], d["Y"], d["I"], d["r_is_a"] = O, X, M, Y, I, r_is_a
+                La, Lb = n // Y, n // X
+                d["La"], d["Lb"] = La, Lb
+                fac_a, fac_b = (t.fac_r, t.fac_c) if r_is_a else (t.fac_c, t.fac_r)
+                d["fac_a"], d["fac_b"] = fac_a.data_ptr(), fac_b.data_ptr()
+                rshape = list(t.fac_r.shape)
+                ax = t.rcm_axis
+                d["rcm_pre"], d["rcm_A"], d["rcm_post"] = _prod(rshape[:ax]), rshape[ax], _prod(rshape[ax + 1:])
+                fast = (O == 1 and M == 1 and I == 1 and Y % 4 == 0 and n < 2**31
+                        and not (t.slice_last2 and t.p.dim() > 2) and _aligned16(t.p, t.m, t.v, t.out))
+                d["mode"] = L.MODE_FAST2D if fast else L.MODE_GENERIC
+                ws_items += [("t", i, "f_a", 3 * La), ("t", i, "f_b", 3 * Lb), ("t", i, "sum_a", La), ("t", i, "sum_b", Lb)]
+                if fast:
+                    rb = max(8, ((X + 63) // 64 + 7) // 8 * 8)
+                    n_strips = (X + rb - 1) // rb
+                    n_cb = (Y + L.A_COLS - 1) // L.A_COLS
+                    d["rb"], d["n_strips"], d["n_cb"] = rb, n_strips, n_cb
+                    ws_items += [("t", i, "fx", 4 * La), ("t", i, "part_a", X * n_cb), ("t", i, "part_b", n_strips * Y),
+                                 ("t", i, "h_a", La * H), ("t", i, "h_b", Lb * H)]
+                    for s in range(n_strips):
+                        for cb in range(n_cb):
+                            atiles.append((i, s, cb, 0))
+                else:
+                    generic.append(i)
+            ws_items.append(("t", i, "closed", L.STAT_STRIDE))
+
+        # units of element-wise work
+        self.sliced = any(t.slice_last2 and t.p.dim() > 2 for t in tensors)
+        unit_owner = []  # (tensor index, element offset)
+        for i, t in enumerate(tensors):
+            if t.slice_last2 and t.p.dim() > 2:
+                mat = t.p.shape[-1] * t.p.shape[-2]
+                unit_owner += [(i, k * mat) for k in range(t.p.numel() // mat)]
+            else:
+                unit_owner.append((i, 0))
+        U = len(unit_owner)
+        if self.sliced:
+            udesc = np.zeros(U, dtype=L.DESC_DTYPE)
+            for u, (i, off) in enumerate(unit_owner):
+                udesc[u] = tdesc[i]
+                t = tensors[i]
+                if t.slice_last2 and t.p.dim() > 2:
+                    mat = t.p.shape[-1] * t.p.shape[-2]
+                    udesc["n"][u], udesc["idx0"][u], udesc["vec_elementwise"][u] = mat, off, 1
+                    for f in ("p", "m", "v", "out"):
+                        if udesc[f][u]:
+                            udesc[f][u] += 4 * off
+                    ws_items.append(("u", u, "closed", L.STAT_STRIDE))  # stays zero: no closed forms for a slice
+        else:
+            udesc = tdesc
+        sizes = [int(udesc["n"][u]) for u in range(U)]
+        tiles, ranges = make_tiles(sizes)
+        for u, (t0, k) in enumerate(ranges):
+            udesc["tile0"][u], udesc["n_tiles"][u] = t0, k
+            ws_items += [("u", u, "sums", L.SUMS_STRIDE), ("u", u, "wfold", L.WFOLD_STRIDE),
+                         ("u", u, "tile_part", k * L.STAT_STRIDE)]
+        # workspace: every sub-buffer starts on a 256-byte boundary
+        off = 0
+        placed = []
+        for table, row, fld, count in ws_items:
+            placed.append((table, row, fld, off))
+            off += (count + 63) // 64 * 64
+        self.workspace = torch.zeros(max(off, 64), dtype=torch.float32, device=self.device)
+        base = self.workspace.data_ptr()
+        for table, row, fld, o in placed:
+            (tdesc if table == "t" else udesc)[fld][row] = base + 4 * o
+        if self.sliced:  # units inherit their tensor's factor workspace
+            for u, (i, _) in enumerate(unit_owner):
+                for f in ("f_a", "f_b", "fx", "sum_a", "sum_b", "part_a", "part_b", "h_a", "h_b"):
+                    udesc[f][u] = tdesc[f][i]
+                if not udesc["vec_elementwise"][u]:
+                    udesc["closed"][u] = tdesc["closed"][i]
+        self.unit_owner = unit_owner
+        self.tdesc = DeviceTable(tdesc, self.device)
+        self.desc = DeviceTable(udesc, self.device) if self.sliced else self.tdesc
+        self.tiles = DeviceTable(tiles, self.device)
+        self.n_tiles = len(tiles)
+        self.atiles = DeviceTable(np.array(atiles, dtype=np.int32).reshape(-1, 4).view(L.ATILE_DTYPE).reshape(-1), self.device)
+        self.n_atiles = len(atiles)
+        self.generic = DeviceTable(np.array(generic, dtype=np.int32), self.device)
+        self.n_generic = len(generic)
+        self.n_tensors = T
+        self.n_units = U
+        self.total_elems = int(sum(sizes))
+        self._keepalive = []
+
+    # ------------------------------------------------------------------ per-step refresh
+    def set_field(self, name, values):
+        """Set a per-tensor field (scalar or one value per tensor) in both tables."""
+        self.tdesc.host[name][:] = values
+        if self.sliced:
+            vals = np.broadcast_to(np.asarray(values), (self.n_tensors,))
+            self.desc.host[name][:] = [vals[i] for i, _ in self.unit_owner]
+
+    def refresh(self, grads: Sequence[torch.Tensor], steps=None):
+        """Point the descriptors at this step's gradients (and step counts) and upload the tables."""
+        self._keepalive = []
+        ptrs = np.zeros(self.n_tensors, dtype=np.uint64)
+        for i, g in enumerate(grads):
+            if not (g.is_cuda and g.dtype == torch.float32 and g.is_contiguous() and g.data_ptr() % 16 == 0):
+                g = g.to(torch.float32).contiguous().clone()
+                self._keepalive.append(g)
+            ptrs[i] = g.data_ptr()
+        self.tdesc.host["g"][:] = ptrs
+        if steps is not None:
+            self.set_field("step", steps)
+        self.tdesc.upload()
+        if self.sliced:
+            self.desc.host["g"][:] = [ptrs[i] + np.uint64(4 * off) for i, off in self.unit_owner]
+            self.desc.upload()
+
+    # ------------------------------------------------------------------ launch sequence
+    def run_front(self, prm: L.StepParams, stream: int, reverse_b: bool = True):
+        """Phases A, A2, B, B2."""
+        pp = C.byref(prm)
+        if self.n_atiles or self.n_generic:
+            L.check(L.lib.pylo_b200_rowcol_sums(self.tdesc.ptr, self.atiles.ptr, self.n_atiles, self.generic.ptr,
+                                                self.n_generic, pp, stream), "rowcol_sums")
+        L.check(L.lib.pylo_b200_factor_update(self.tdesc.ptr, self.n_tensors, pp, stream), "factor_update")
+        L.check(L.lib.pylo_b200_state_moments(self.desc.ptr, self.tiles.ptr, self.n_tiles, int(reverse_b), pp, stream), "state_moments")
+        L.check(L.lib.pylo_b200_finalize_moments(self.desc.ptr, self.n_units, stream), "finalize_moments")
+
+    def run_back(self, prm: L.StepParams, stream: int, reverse_c: bool = False):
+        """Phases P, C."""
+        pp = C.byref(prm)
+        L.check(L.lib.pylo_b200_prep_apply(self.desc.ptr, self.n_units, pp, stream), "prep_apply")
+        L.check(L.lib.pylo_b200_apply(self.desc.ptr, self.tiles.ptr, self.n_tiles, int(reverse_c), pp, stream), "apply")
+
+
+class GradNorm:
+    """Device-side sum of squares of a list of gradients (the global-norm clip)."""
+
+    def __init__(self, sizes: Sequence[int], device):
+        self.items = np.zeros(len(sizes), dtype=L.GVEC_DTYPE)
+        self.items["n"] = sizes
+        tiles, _ = make_tiles(sizes)
+        self.tiles = DeviceTable(tiles, device)
+        self.n_tiles = len(tiles)
+        self.table = DeviceTable(self.items, device)
+        self.scratch = torch.zeros(max(self.n_tiles, 1), dtype=torch.float32, device=device)
+        self.out = torch.zeros(1, dtype=torch.float32, device=device)
+        self._keepalive = []
+
+    def run(self, grads: Sequence[torch.Tensor], stream: int):
+        self._keepalive = []
+        for i, g in enumerate(grads):
+            if not (g.dtype == torch.float32 and g.is_contiguous()):
+                g = g.to(torch.float32).contiguous()
+                self._keepalive.append(g)
+            self.items["g"][i] = g.data_ptr()
+        self.table.upload()
+        L.check(L.lib.pylo_b200_grad_sumsq(self.table.ptr, self.tiles.ptr, self.n_tiles, self.scratch.data_ptr(),
+                                           self.out.data_ptr(), stream), "grad_sumsq")
+        return self.out
+
+
+def current_stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def f32(x) -> float:
+    """Round a Python float to fp32 the way a torch fp32 tensor element would hold it."""
+    return float(np.float32(x))
+
+
+def one_minus(beta: torch.Tensor) -> List[float]:
+    """``1 - beta`` evaluated in fp32, as ``1 - tensor`` does in the reference classes."""
+    return [float(x) for x in (1 - beta.detach().to("cpu", torch.float32)).tolist()]
+
+
+INF = math.inf
