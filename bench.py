@@ -1,0 +1,410 @@
+#!/usr/bin/env python
+"""Benchmark of the learned-optimizer step on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+                    [--workload llama3_8b|gpt2_medium|vit_b16|celo2_4096|mlp_784] [--optimizer adafaclo|...]
+
+One "step" is one ``optimizer.step()`` over every parameter tensor of the
+workload (plus, with more than one GPU, the all-gather of the updated
+parameters).  Tensors are owned ZeRO-1 style by one rank each, so the total
+work is fixed as N grows (strong scaling).  Prints ONE JSON line on rank 0.
+
+``--impl reference`` times the CPU restatement of the reference's step
+(oracle/pylo_oracle.py) on the host cores of the box, on a bounded sample of the
+same workload; it is the only place besides the ``cpu_baseline`` leg where this
+script executes anything under oracle/.
+"""
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "optimizer_step_params_per_sec"
+UNIT = "params/s"
+# compulsory HBM bytes per parameter of a whole step: g, p, m(3), v read once; p, m(3), v written once
+STEP_BYTES = {"adafaclo": 44, "elo": 44, "velo": 44, "celo2": 56, "elo_celo2": 56}
+# compulsory bytes per parameter of the apply sweep alone (reads g, p, m(3), v; writes p or the raw step)
+APPLY_BYTES = 28
+B_BYTES = 40  # state_moments sweep: reads g, p, m(3), v; writes m(3), v
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="llama3_8b")
+    ap.add_argument("--optimizer", default="adafaclo", choices=sorted(STEP_BYTES))
+    ap.add_argument("--layers", type=int, default=None, help="llama3_8b only: number of transformer layers (default 32)")
+    ap.add_argument("--no-orthogonalize", action="store_true", help="celo2 family: skip Newton-Schulz")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-sample-steps", type=int, default=3)
+    return ap.parse_args()
+
+
+def workload_shapes(args):
+    from pylo_b200 import workloads as W
+
+    if args.workload == "llama3_8b":
+        return W.llama3_8b(args.layers or 32)
+    return W.WORKLOADS[args.workload]()
+
+
+def grad_spec(args):
+    return {"llama3_8b": (1e-4, "iid"), "gpt2_medium": (1e-3, "outliers"), "vit_b16": (1e-3, "iid"),
+            "celo2_4096": (1.0, "rowlognormal"), "mlp_784": (1e-3, "iid")}[args.workload]
+
+
+def seeded_networks(kind):
+    from pylo_b200 import models
+
+    torch.manual_seed(0)
+    if kind in ("adafaclo", "elo"):
+        return models.MetaMLP(39, 32, 1)
+    if kind in ("celo2", "elo_celo2"):
+        return models.CELO2MLP()
+    rnn, mlp = models.VeLORNN(), models.VeLOMLP()
+    with torch.no_grad():
+        for name, p in mlp.named_parameters():
+            if name.endswith("_") or "_." in name:
+                p.mul_(0.05)  # the banks are N(0,1) by default and get multiplied by 100 when mixed
+    return rnn, mlp
+
+
+def build_optimizer(args, params, is_embedding=None):
+    from pylo_b200 import optim
+
+    k = args.optimizer
+    if k == "adafaclo":
+        return optim.AdafacLO_CUDA(params, lr=1e-3, step_mult=0.01, exp_mult=0.001, network=seeded_networks(k))
+    if k == "elo":
+        return optim.ELO_CUDA(params, lr=1e-3, weight_decay=0.1, clip_grad=True, network=seeded_networks(k))
+    if k in ("celo2", "elo_celo2"):
+        groups = [{"params": [p for p, e in zip(params, is_embedding) if not e]},
+                  {"params": [p for p, e in zip(params, is_embedding) if e], "is_embedding": True}]
+        groups = [g for g in groups if g["params"]]
+        cls = optim.CELO2_CUDA if k == "celo2" else optim.ELO_CELO2_CUDA
+        kw = dict(lr=1e-3, weight_decay=0.1, orthogonalize=not args.no_orthogonalize, network=seeded_networks(k))
+        return cls(groups, **kw)
+    rnn, mlp = seeded_networks(k)
+    return optim.VeLO_CUDA(params, lr=1e-3, num_steps=10000, rnn=rnn, mlp=mlp)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sample_shapes(args, shapes):
+    """A bounded sample of the workload for the CPU legs: one mid-sized matrix and one vector of it."""
+    mats = sorted({s for s in shapes if len(s) >= 2}, key=lambda s: abs(s[0] * s[1] - 4_194_304) if len(s) == 2 else 1e18)
+    vecs = sorted({s for s in shapes if len(s) == 1})
+    sample = [mats[0]] + ([vecs[0]] if vecs else [])
+    return sample
+
+
+def run_cpu_oracle(args, shapes, steps, warmup=1):
+    """Time the oracle's step on the host cores; returns (params/s, cores, sample description)."""
+    from oracle import pylo_oracle as O
+    from pylo_b200 import workloads as W
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    sample = cpu_sample_shapes(args, shapes)
+    gscale, gkind = grad_spec(args)
+    gen = torch.Generator().manual_seed(1)
+    params = [torch.randn(s, generator=gen) * 0.02 for s in sample]
+    grads = [torch.randn(s, generator=gen) * gscale for s in sample]
+    k = args.optimizer
+    if k in ("adafaclo", "elo"):
+        net = seeded_networks(k)
+        o = O.AdafacLOOracle(net.flat_weights(), lr=1e-3, elo=(k == "elo"), weight_decay=0.1 if k == "elo" else 0.0,
+                             clip_grad=(k == "elo"))
+        step = lambda: o.step(params, grads)
+    elif k in ("celo2", "elo_celo2"):
+        net = seeded_networks(k)
+        o = O.CELO2Oracle(net.flat_weights(), lr=1e-3, weight_decay=0.1, orthogonalize=not args.no_orthogonalize,
+                          shared_adam=(k == "elo_celo2"), clip_grad=(k == "elo_celo2"),
+                          adam_lr_mult=20.0 if k == "elo_celo2" else 1.0)
+        step = lambda: o.step(params, grads)
+    else:
+        rnn, mlp = seeded_networks(k)
+        o = O.VeLOOracle(O.rnn_weights_from_module(rnn), O.bank_from_module(mlp), sample, lr=1e-3, num_steps=10000)
+        step = lambda: o.step(params, grads, 1.0)
+    for _ in range(warmup):
+        step()
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    n = W.total_params(sample)
+    mean = sum(times) / len(times)
+    desc = f"{' + '.join(str(s) for s in sample)} of the workload, {steps} step(s) after {warmup} warm-up"
+    return n / mean, torch.get_num_threads(), desc, mean
+
+
+def config_of(args, shapes, n_gpus):
+    from pylo_b200 import workloads as W
+
+    gscale, gkind = grad_spec(args)
+    return {
+        "workload": f"{args.optimizer} step over {args.workload} parameter shapes ({len(shapes)} tensors, "
+                    f"{W.total_params(shapes) / 1e9:.3f} G fp32 params), ZeRO-1 whole-tensor ownership",
+        "optimizer": args.optimizer, "shapes": args.workload, "tensors": len(shapes),
+        "params": W.total_params(shapes), "grads": f"randn*{gscale} ({gkind}), one buffer per distinct shape",
+        "orthogonalize": (not args.no_orthogonalize) if "celo2" in args.optimizer else None,
+        "cache": "inputs larger than L2 (no flush needed)" if W.total_params(shapes) * 24 / max(n_gpus, 1) > 2e9
+                 else "L2 flushed between steps by writing a 512 MiB buffer",
+        "parallelism": f"zero1x{n_gpus}",
+    }
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    shapes = workload_shapes(args)
+    steps = max(1, args.steps)
+    value, cores, desc, mean = run_cpu_oracle(args, shapes, steps, warmup=max(1, min(args.warmup, 2)))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": mean * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_of(args, shapes, args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def run_b200(args):
+    import torch.distributed as dist
+
+    from pylo_b200 import workloads as W
+    from pylo_b200.zero import ShardedStep
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    shapes = workload_shapes(args)
+    total = W.total_params(shapes)
+    gscale, gkind = grad_spec(args)
+
+    # memory guard: never drive the box out of memory
+    free, _ = torch.cuda.mem_get_info()
+    state_bytes = 16 if args.optimizer not in ("celo2", "elo_celo2") else 20
+    need = total * 4 + (total / world) * (state_bytes + 1) * 1.02 + 4e9
+    if need > free * 0.97:
+        raise SystemExit(f"workload needs ~{need / 1e9:.0f} GB per GPU, {free / 1e9:.0f} GB free: refusing to run")
+
+    shard = ShardedStep.from_shapes(shapes, dev, init_scale=0.02, seed=1)
+    owned = shard.owned
+    params = [shard.params[i] for i in owned]
+    pool = W.make_grad_pool([shapes[i] for i in owned], gscale, dev, seed=2 + rank, kind=gkind)
+    for p in params:
+        p.grad = pool[tuple(p.shape)]
+    emb = [shapes[i][0] > 32768 for i in owned]  # token embedding / lm head go to the AdamW branch in the CELO2 family
+    opt = build_optimizer(args, params, emb)
+    owned_n = sum(p.numel() for p in params)
+    velo = args.optimizer == "velo"
+    loss = torch.tensor(1.0, device=dev)
+    flush = None
+    if total * 24 / world <= 2e9:
+        flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+
+    def one_step():
+        if flush is not None:
+            flush.fill_(1)
+        opt.step(loss) if velo else opt.step()
+        shard.gather()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def plans():
+        out = []
+        for v in getattr(opt, "_plans", {}).values():
+            out.append(v[1]["lo"] if isinstance(v[1], dict) else v[1])
+        if getattr(opt, "_plan", None):
+            out.append(opt._plan[1]["plan"])
+        return [p for p in out if p is not None]
+
+    for _ in range(max(args.warmup, 3)):
+        one_step()
+    barrier()
+    for pl in plans():
+        pl.enable_profile(True)
+        pl.launch_count = 0
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    barrier()
+    ev[0].record()
+    for _ in range(args.steps):
+        one_step()
+    ev[1].record()
+    barrier()
+    elapsed_ms = ev[0].elapsed_time(ev[1])
+    clocks = sampler.stop() if rank == 0 else None
+    phase = {}
+    launches = 0
+    for pl in plans():
+        for k, v in pl.phase_times().items():
+            phase.setdefault(k, []).extend(v)
+        launches += pl.launch_count
+        pl.enable_profile(False)
+    t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+    value = total / (ms_per_step * 1e-3)
+
+    # ---- end to end: gradients arrive from pinned host memory, a probe of the result goes back
+    e2e = None
+    if not args.no_e2e:
+        pinned = {s: torch.empty(s, dtype=torch.float32).pin_memory() for s in pool}
+        for s, buf in pinned.items():
+            buf.copy_(pool[s])
+        probe_idx = torch.tensor([shard.offsets[i] for i in owned], device=dev)
+        h2d = sum(p.numel() for p in params) * 4
+        d2h = len(owned) * 4
+
+        def e2e_step():
+            for p in params:
+                p.grad.copy_(pinned[tuple(p.shape)], non_blocking=True)
+            one_step()
+            return shard.flat.index_select(0, probe_idx).cpu()
+
+        e2e_step()
+        barrier()
+        ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        t0 = time.perf_counter()
+        ev2[0].record()
+        for _ in range(args.steps):
+            e2e_step()
+        ev2[1].record()
+        barrier()
+        wall = (time.perf_counter() - t0) * 1e3
+        te = torch.tensor([max(ev2[0].elapsed_time(ev2[1]), wall)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_ms = float(te.item()) / args.steps
+        hb = torch.tensor([h2d, d2h], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(hb)
+        e2e = {"value": total / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": int(hb[0].item()), "d2h_bytes_per_step": int(hb[1].item())}
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
+        mean = lambda xs: sum(xs) / max(len(xs), 1)
+        phase_ms = {k: mean(v) for k, v in phase.items()}
+        phase_share = {k: sum(v) for k, v in phase.items()}
+        dominant = max(phase_share, key=phase_share.get) if phase_share else None
+        lo_elems = sum(pl.total_elems for pl in plans())
+        n_launch = max(len(phase.get(dominant, [])), 1)
+        per_launch_elems = lo_elems * args.steps / n_launch if dominant else 0
+        kbytes = {"apply": APPLY_BYTES, "state_moments": B_BYTES, "rowcol_sums": 4}.get(dominant, 0)
+        achieved = per_launch_elems * kbytes / (phase_ms.get(dominant, 1e9) * 1e-3) / 1e9 if dominant else 0.0
+        roofline = {
+            "bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "peak_source": f"{peak_src} (MEASURED_PEAKS.json hbm_gbs)", "traffic": None,
+            "algorithmic_bytes_per_param": kbytes, "avg_launch_ms": phase_ms.get(dominant),
+            "phase_ms_per_launch": phase_ms,
+            "step": {"algorithmic_bytes_per_param": STEP_BYTES[args.optimizer],
+                     "achieved": owned_n * STEP_BYTES[args.optimizer] / (ms_per_step * 1e-3) / 1e9,
+                     "frac": owned_n * STEP_BYTES[args.optimizer] / (ms_per_step * 1e-3) / 1e9 / peak},
+        }
+        if args.optimizer in ("adafaclo", "elo") and dominant == "apply" and clocks and clocks.get("sm_mhz"):
+            # the apply sweep of the 39-32-32-2 network is bound by fp32 FMA issue, not by HBM
+            fma = per_launch_elems * 1600 / (phase_ms[dominant] * 1e-3)
+            peak_fma = 148 * 128 * clocks["sm_mhz"] * 1e6
+            roofline["fp32_fma"] = {"fma_per_param": 1600, "achieved_tfma": fma / 1e12,
+                                    "peak_tfma_at_sampled_clock": peak_fma / 1e12, "frac": fma / peak_fma}
+        cpu = None
+        if not args.no_cpu_baseline and world == 1:
+            v, cores, desc, _ = run_cpu_oracle(args, shapes, args.cpu_sample_steps)
+            cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_of(args, shapes, world),
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -265,21 +265,47 @@ class LoPlan:
             self.desc.upload()
 
     # ------------------------------------------------------------------ launch sequence
+    #: kernels each C-ABI call launches (for the launch count the benchmark reports)
+    LAUNCHES = {"rowcol_sums": 1, "factor_update": 1, "state_moments": 1, "finalize_moments": 1,
+                "prep_apply": 1, "apply": 1}
+
+    def enable_profile(self, on: bool = True):
+        """Record a CUDA-event pair around every phase launch (read back with :meth:`phase_times`)."""
+        self._prof = {} if on else None
+
+    def phase_times(self):
+        """{phase: [ms, ...]} of the recorded launches; call after a device synchronisation."""
+        return {k: [a.elapsed_time(b) for a, b in v] for k, v in (self._prof or {}).items()}
+
+    def _call(self, name, fn, *args):
+        prof = getattr(self, "_prof", None)
+        if prof is not None:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+        L.check(fn(*args), name)
+        self.launch_count = getattr(self, "launch_count", 0) + self.LAUNCHES[name]
+        if prof is not None:
+            b.record()
+            prof.setdefault(name, []).append((a, b))
+
     def run_front(self, prm: L.StepParams, stream: int, reverse_b: bool = True):
         """Phases A, A2, B, B2."""
         pp = C.byref(prm)
         if self.n_atiles or self.n_generic:
-            L.check(L.lib.pylo_b200_rowcol_sums(self.tdesc.ptr, self.atiles.ptr, self.n_atiles, self.generic.ptr,
-                                                self.n_generic, pp, stream), "rowcol_sums")
-        L.check(L.lib.pylo_b200_factor_update(self.tdesc.ptr, self.n_tensors, pp, stream), "factor_update")
-        L.check(L.lib.pylo_b200_state_moments(self.desc.ptr, self.tiles.ptr, self.n_tiles, int(reverse_b), pp, stream), "state_moments")
-        L.check(L.lib.pylo_b200_finalize_moments(self.desc.ptr, self.n_units, stream), "finalize_moments")
+            self._call("rowcol_sums", L.lib.pylo_b200_rowcol_sums, self.tdesc.ptr, self.atiles.ptr, self.n_atiles,
+                       self.generic.ptr, self.n_generic, pp, stream)
+            if self.n_atiles and self.n_generic:
+                self.launch_count += 1
+        self._call("factor_update", L.lib.pylo_b200_factor_update, self.tdesc.ptr, self.n_tensors, pp, stream)
+        self._call("state_moments", L.lib.pylo_b200_state_moments, self.desc.ptr, self.tiles.ptr, self.n_tiles,
+                   int(reverse_b), pp, stream)
+        self._call("finalize_moments", L.lib.pylo_b200_finalize_moments, self.desc.ptr, self.n_units, stream)
 
     def run_back(self, prm: L.StepParams, stream: int, reverse_c: bool = False):
         """Phases P, C."""
         pp = C.byref(prm)
-        L.check(L.lib.pylo_b200_prep_apply(self.desc.ptr, self.n_units, pp, stream), "prep_apply")
-        L.check(L.lib.pylo_b200_apply(self.desc.ptr, self.tiles.ptr, self.n_tiles, int(reverse_c), pp, stream), "apply")
+        self._call("prep_apply", L.lib.pylo_b200_prep_apply, self.desc.ptr, self.n_units, pp, stream)
+        self._call("apply", L.lib.pylo_b200_apply, self.desc.ptr, self.tiles.ptr, self.n_tiles, int(reverse_c), pp, stream)
 
 
 class GradNorm:

@@ -1,0 +1,118 @@
+"""ZeRO-1 style sharding of the optimizer step across the GPUs of one box.
+
+Every reduction of the learned-optimizer step is per tensor (row/column sums,
+feature normalisers, the CELO2 tail, Newton-Schulz), so a rank that owns a
+whole tensor needs nothing from the others to update it.  Ownership is
+therefore whole-tensor: a deterministic longest-processing-time assignment by
+cost.  Parameters live in one flat fp32 buffer laid out
+``[rank 0's tensors | pad][rank 1's tensors | pad]...`` with equal-sized rank
+regions; after the local step one in-place ``all_gather_into_tensor`` over NCCL
+(NVLink / NVSwitch) makes every rank's copy complete again.  The global-norm
+clip adds one scalar ``all_reduce``.
+
+The reference has no distributed code; its documentation describes exactly this
+scheme in prose (docs/concepts.rst:274-283).
+"""
+
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+ALIGN = 64  # floats; every tensor starts on a 256-byte boundary inside the flat buffer
+
+
+def _numel(shape) -> int:
+    n = 1
+    for d in shape:
+        n *= int(d)
+    return n
+
+
+def partition(shapes: Sequence[Tuple[int, ...]], world_size: int,
+              cost: Optional[Callable[[Tuple[int, ...]], float]] = None) -> List[int]:
+    """Owner rank of every tensor: greedy longest-processing-time, ties by index; deterministic."""
+    cost = cost or (lambda s: float(_numel(s)))
+    order = sorted(range(len(shapes)), key=lambda i: (-cost(shapes[i]), i))
+    load = [0.0] * world_size
+    owner = [0] * len(shapes)
+    for i in order:
+        r = min(range(world_size), key=lambda k: (load[k], k))
+        owner[i] = r
+        load[r] += cost(shapes[i])
+    return owner
+
+
+def flat_layout(shapes: Sequence[Tuple[int, ...]], owner: Sequence[int], world_size: int):
+    """Offsets (in floats) of every tensor in the flat buffer and the per-rank region size."""
+    used = [0] * world_size
+    local = [0] * len(shapes)
+    for i, s in enumerate(shapes):
+        r = owner[i]
+        local[i] = used[r]
+        used[r] += (_numel(s) + ALIGN - 1) // ALIGN * ALIGN
+    shard = max(max(used), ALIGN)
+    offsets = [owner[i] * shard + local[i] for i in range(len(shapes))]
+    return offsets, shard
+
+
+class ShardedStep:
+    """Flat parameter buffer + ownership + the post-step gather for one process group.
+
+    ``params`` are ``nn.Parameter``s (or tensors) in a fixed global order that is
+    identical on every rank; their ``.data`` is re-pointed into the flat buffer.
+    ``owned`` lists the indices this rank updates; build the optimizer over
+    ``[params[i] for i in owned]`` and call :meth:`gather` after ``optimizer.step()``.
+    """
+
+    def __init__(self, params: Sequence[torch.Tensor], process_group=None,
+                 cost: Optional[Callable[[Tuple[int, ...]], float]] = None, copy_values: bool = True):
+        self.pg = process_group
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+        self.params = list(params)
+        shapes = [tuple(p.shape) for p in self.params]
+        self.owner = partition(shapes, self.world, cost)
+        self.offsets, self.shard = flat_layout(shapes, self.owner, self.world)
+        dev = self.params[0].device
+        self.flat = torch.zeros(self.shard * self.world, dtype=torch.float32, device=dev)
+        for p, off, s in zip(self.params, self.offsets, shapes):
+            view = self.flat[off:off + _numel(s)].view(s)
+            if copy_values:
+                view.copy_(p.data)
+            p.data = view
+        self.owned = [i for i, r in enumerate(self.owner) if r == self.rank]
+
+    @classmethod
+    def from_shapes(cls, shapes: Sequence[Tuple[int, ...]], device, init_scale: float = 0.02, seed: int = 1,
+                    process_group=None, cost=None) -> "ShardedStep":
+        """Allocate the flat buffer first and create the parameters as seeded views into it
+        (no second copy of the parameters ever exists)."""
+        self = cls.__new__(cls)
+        self.pg = process_group
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+        shapes = [tuple(s) for s in shapes]
+        self.owner = partition(shapes, self.world, cost)
+        self.offsets, self.shard = flat_layout(shapes, self.owner, self.world)
+        self.flat = torch.zeros(self.shard * self.world, dtype=torch.float32, device=device)
+        gen = torch.Generator(device=device)
+        self.params = []
+        for i, (off, s) in enumerate(zip(self.offsets, shapes)):
+            view = self.flat[off:off + _numel(s)].view(s)
+            gen.manual_seed(seed * 1000003 + i)
+            view.normal_(0.0, init_scale, generator=gen)
+            self.params.append(torch.nn.Parameter(view, requires_grad=True))
+        self.owned = [i for i, r in enumerate(self.owner) if r == self.rank]
+        return self
+
+    def my_region(self) -> torch.Tensor:
+        return self.flat[self.rank * self.shard:(self.rank + 1) * self.shard]
+
+    def gather(self, async_op: bool = False):
+        """All-gather every rank's region in place; afterwards all ranks hold all updated parameters."""
+        if self.world == 1:
+            return None
+        return dist.all_gather_into_tensor(self.flat, self.my_region(), group=self.pg, async_op=async_op)
