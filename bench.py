@@ -366,7 +366,7 @@ def run_b200(args):
         lo_elems = sum(pl.total_elems for pl in plans())
         n_launch = max(len(phase.get(dominant, [])), 1)
         per_launch_elems = lo_elems * args.steps / n_launch if dominant else 0
-        kbytes = {"apply": APPLY_BYTES, "state_moments": B_BYTES, "rowcol_sums": 4}.get(dominant, 0)
+        kbytes = {"apply": APPLY_BYTES, "apply_cols": APPLY_BYTES, "state_moments": B_BYTES, "rowcol_sums": 4}.get(dominant, 0)
         achieved = per_launch_elems * kbytes / (phase_ms.get(dominant, 1e9) * 1e-3) / 1e9 if dominant else 0.0
         roofline = {
             "bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -377,7 +377,7 @@ def run_b200(args):
                      "achieved": owned_n * STEP_BYTES[args.optimizer] / (ms_per_step * 1e-3) / 1e9,
                      "frac": owned_n * STEP_BYTES[args.optimizer] / (ms_per_step * 1e-3) / 1e9 / peak},
         }
-        if args.optimizer in ("adafaclo", "elo") and dominant == "apply" and clocks and clocks.get("sm_mhz"):
+        if args.optimizer in ("adafaclo", "elo") and dominant in ("apply", "apply_cols") and clocks and clocks.get("sm_mhz"):
             # the apply sweep of the 39-32-32-2 network is bound by fp32 FMA issue, not by HBM
             fma = per_launch_elems * 1600 / (phase_ms[dominant] * 1e-3)
             peak_fma = 148 * 128 * clocks["sm_mhz"] * 1e6

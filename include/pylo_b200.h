@@ -190,6 +190,14 @@ int pylo_b200_prep_apply(const pylo_tensor_desc* descs, int n_tensors, const pyl
 int pylo_b200_apply(const pylo_tensor_desc* descs, const pylo_tile* tiles, int n_tiles, int reverse,
                     const pylo_step_params* prm, void* stream);
 
+/* Phase C for the FAST2D tensors of the ADAFAC family (same arithmetic as pylo_b200_apply, organised for
+ * the FMA-bound 39-32-32-2 network: a thread keeps one column, packed fp32x2 FMAs).  ctiles: one entry per
+ * tile with strip = row-tile index, cb = column-tile index, pad_ = columns per CTA (32, 64, 128 or 256); a tile
+ * has 16 rows at 256 columns and 32 rows otherwise.  With this kernel in use pylo_b200_apply gets only the non-FAST2D tiles.
+ * For this family pylo_b200_prep_apply stores desc.h_b transposed, [32][Y]. */
+int pylo_b200_apply_adafac_cols(const pylo_tensor_desc* descs, const pylo_atile* ctiles, int n_ctiles,
+                                const pylo_step_params* prm, void* stream);
+
 /* CELO2 tail (CELO2_cuda.py:336-339): step * rsqrt(mean(step^2 over the last two axes) + 1e-9) * rmsmult,
  * then p -= lr * (step + wd * p).  Items are matrices (the last two axes of a tensor). */
 typedef struct pylo_post_item {

@@ -90,6 +90,7 @@ def _load():
         "pylo_b200_finalize_moments": [vp, i32, vp],
         "pylo_b200_prep_apply": [vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_apply": [vp, vp, i32, i32, C.POINTER(StepParams), vp],
+        "pylo_b200_apply_adafac_cols": [vp, vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_celo2_post_sums": [vp, vp, i32, vp],
         "pylo_b200_celo2_post_apply": [vp, vp, i32, vp],
         "pylo_b200_adamw": [vp, vp, i32, i32, f32, f32, f32, f32, f32, C.POINTER(StepParams), vp],

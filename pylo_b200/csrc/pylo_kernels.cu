@@ -563,7 +563,8 @@ __global__ void __launch_bounds__(NT) k_prep_apply(const pylo_tensor_desc* __res
       acc = fmaf(s_w1[(kb + k) * H + j], r, acc);
       acc = fmaf(s_w1[(krb + k) * H + j], rsqrtf(r + 1e-8f), acc);
     }
-    d.h_b[e] = acc;
+    if (FAM == PYLO_FAM_ADAFAC) d.h_b[(int64_t)j * Lb + i] = acc;  // transposed for the column kernel
+    else d.h_b[e] = acc;
   }
 }
 
@@ -761,6 +762,241 @@ __global__ void __launch_bounds__(NT) k_apply(const pylo_tensor_desc* __restrict
         for (int j = 0; j < H; ++j) h1[0][j] = s_w[L::B1 + j];
         network<FAM, true, 1>(s_wa, h1, f, o0, o1);
         op[i] = finish<FAM>(p, o0[0], o1[0], d, param_scale, lr_eff, prm.wd_mode);
+      }
+    }
+  }
+}
+
+// ================================================================================================
+// Phase C for AdafacLO / ELO on FAST2D tensors: thread-owns-column kernel.
+//
+// The 39-32-32-2 network costs ~1600 fp32 FMAs per element once the vector-only features and
+// the time features are folded away, so this sweep is bound by FMA issue, not by HBM.  Layout:
+//   * a CTA takes a tile of RT rows x CW columns; a thread keeps ONE column for all its rows, so
+//     the column's tabulated first-layer term (32 floats) and its three column factors stay in
+//     registers, and the rows' terms sit in shared memory;
+//   * two rows are processed at once so every weight read from shared memory feeds two elements;
+//   * all multiply-adds are packed fma.rn.f32x2 (two fp32 FMAs per instruction) over pairs of
+//     adjacent hidden units, which halves the issue slots the FMAs need;
+//   * the first hidden layer's activations are staged through shared memory so that the second
+//     layer can run as a short loop over k instead of 1000+ unrolled instructions;
+//   * the next pair's operands are loaded while the current pair is computed.
+// ================================================================================================
+#define CC_TILE_ROWS 32   // rows per tile when a CTA is narrower than 256 columns (16 rows at 256 columns)
+
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+#define CC_E 2            // rows a thread processes at once (each weight read feeds CC_E elements)
+#define CC_CTAS_PER_SM 2  // 128 registers per thread
+
+struct CcSmem {
+  float w[Fold<PYLO_FAM_ADAFAC>::SIZE + 12];  // folded network
+  float ha[CC_TILE_ROWS][32];                 // first-layer terms of the tile's rows (bias included)
+  float fx[CC_TILE_ROWS][4];                  // the rows' three factors
+  float hb[16][NT][2];                        // first-layer terms of the tile's columns, hidden-unit pairs
+  float h1[32][NT][CC_E];                     // staged first-layer activations of the rows in flight
+};
+
+__global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const pylo_tensor_desc* __restrict__ descs,
+                                                              const pylo_atile* __restrict__ ctiles, int n_ctiles,
+                                                              const pylo_step_params prm) {
+  using F = Fam<PYLO_FAM_ADAFAC>;
+  using L = Fold<PYLO_FAM_ADAFAC>;
+  constexpr int E = CC_E;
+  extern __shared__ __align__(16) unsigned char cc_raw[];
+  CcSmem& sm = *reinterpret_cast<CcSmem*>(cc_raw);
+  const int tid = threadIdx.x;
+  int loaded = -1;
+  for (int t = blockIdx.x; t < n_ctiles; t += gridDim.x) {
+    const pylo_atile ct = ctiles[t];
+    const pylo_tensor_desc& d = descs[ct.tensor];
+    const int X = d.X, Y = d.Y;
+    const int cw = ct.pad_;                          // columns per CTA: 32, 64, 128 or 256
+    const int ng = NT / cw;                          // row groups
+    const int rt = cw == NT ? 16 : CC_TILE_ROWS;     // rows per tile
+    const int rows_per_thread = rt / ng;             // 16, 16, 8 or 4
+    const int x0 = ct.strip * rt, y0 = ct.cb * cw;
+    const int col = tid % cw, rg = tid / cw;
+    const int y = y0 + col;
+    const bool colok = y < Y;
+    const int yc = colok ? y : 0;
+    __syncthreads();
+    if (loaded != ct.tensor) {
+      for (int e = tid; e < L::SIZE; e += NT) sm.w[e] = d.wfold[e];
+      loaded = ct.tensor;
+    }
+    for (int e = tid; e < rt * 32; e += NT) {
+      const int r = e >> 5, x = x0 + r;
+      sm.ha[r][e & 31] = x < X ? d.h_a[(int64_t)x * 32 + (e & 31)] : 0.f;
+    }
+    for (int e = tid; e < rt * 4; e += NT) {
+      const int r = e >> 2, x = x0 + r;
+      sm.fx[r][e & 3] = x < X ? d.fx[(int64_t)x * 4 + (e & 3)] : 0.f;
+    }
+    // this column's first-layer term (stored transposed, [32][Y]); each thread keeps its own slot
+#pragma unroll 4
+    for (int j = 0; j < 16; ++j) {
+      sm.hb[j][tid][0] = d.h_b[(int64_t)(2 * j) * Y + yc];
+      sm.hb[j][tid][1] = d.h_b[(int64_t)(2 * j + 1) * Y + yc];
+    }
+    __syncthreads();
+    const float fb0 = d.f_b[yc], fb1 = d.f_b[Y + yc], fb2 = d.f_b[2 * (int64_t)Y + yc];
+    const float gs = grad_scale_of(d, prm);
+    const float lr_eff = sm.w[L::SC + 1];
+    const int64_t n = d.n;
+    const float* __restrict__ gp = d.g;
+    float* __restrict__ pp = d.p;
+    const float* __restrict__ mp = d.m;
+    const float* __restrict__ vp = d.v;
+
+    float cg[E], cp[E], cm0[E], cm1[E], cm2[E], cv[E];
+    auto load_rows = [&](int q, float* g, float* p, float* m0, float* m1, float* m2, float* v) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const int x = x0 + rg + ng * (q + e);
+        const bool ok = colok && x < X;
+        const int64_t idx = ok ? (int64_t)x * Y + y : 0;
+        g[e] = __ldg(gp + idx); p[e] = pp[idx]; m0[e] = mp[idx]; m1[e] = mp[n + idx]; m2[e] = mp[2 * n + idx]; v[e] = vp[idx];
+      }
+    };
+    load_rows(0, cg, cp, cm0, cm1, cm2, cv);
+#pragma unroll 1
+    for (int q = 0; q < rows_per_thread; q += E) {
+      float ng_[E], np_[E], nm0[E], nm1[E], nm2[E], nv[E];
+      const bool more = q + E < rows_per_thread;
+      if (more) load_rows(q + E, ng_, np_, nm0, nm1, nm2, nv);
+      // ---- features of the rows in flight
+      float f[E][F::NF];
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const int r = rg + ng * (q + e);
+        const float g = xform_grad(cg[e], gs, prm.clip_val, prm.nan_to_num);
+        const float rs = rsqrtf(cv[e] + prm.eps_feat);
+        const float4 fa = ld4(&sm.fx[r][0]);
+        elem_features<PYLO_FAM_ADAFAC>(f[e], g, cp[e], cm0[e], cm1[e], cm2[e], cv[e], rs, fa.x * fb0, fa.y * fb1, fa.z * fb2);
+      }
+      // ---- first layer in two halves of 16 hidden units
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint64_t h1[E][8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint64_t b = *reinterpret_cast<const uint64_t*>(&sm.hb[half * 8 + j][tid][0]);
+#pragma unroll
+          for (int e = 0; e < E; ++e)
+            h1[e][j] = add2(*reinterpret_cast<const uint64_t*>(&sm.ha[rg + ng * (q + e)][half * 16 + 2 * j]), b);
+        }
+        static_for<0, F::NF>([&](auto kc) {
+          constexpr int k = decltype(kc)::value;
+          if constexpr (!is_vec_feature<PYLO_FAM_ADAFAC>(k)) {
+            uint64_t fk[E];
+#pragma unroll
+            for (int e = 0; e < E; ++e) fk[e] = pack2(f[e][k], f[e][k]);
+            const ulonglong2* wrow = reinterpret_cast<const ulonglong2*>(&sm.w[L::W1 + k * 32 + half * 16]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const ulonglong2 w = wrow[j];
+#pragma unroll
+              for (int e = 0; e < E; ++e) {
+                h1[e][2 * j] = fma2(w.x, fk[e], h1[e][2 * j]);
+                h1[e][2 * j + 1] = fma2(w.y, fk[e], h1[e][2 * j + 1]);
+              }
+            }
+          }
+        });
+        // stage relu(h1), the E rows of one hidden unit side by side, for the second layer's dynamic index
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float lo[E], hi[E];
+#pragma unroll
+          for (int e = 0; e < E; ++e) { unpack2(h1[e][j], lo[e], hi[e]); lo[e] = fmaxf(lo[e], 0.f); hi[e] = fmaxf(hi[e], 0.f); }
+          if constexpr (E == 4) {
+            st4(&sm.h1[half * 16 + 2 * j][tid][0], make_float4(lo[0], lo[1], lo[2], lo[3]));
+            st4(&sm.h1[half * 16 + 2 * j + 1][tid][0], make_float4(hi[0], hi[1], hi[2], hi[3]));
+          } else {
+            *reinterpret_cast<float2*>(&sm.h1[half * 16 + 2 * j][tid][0]) = make_float2(lo[0], lo[1]);
+            *reinterpret_cast<float2*>(&sm.h1[half * 16 + 2 * j + 1][tid][0]) = make_float2(hi[0], hi[1]);
+          }
+        }
+      }
+      // ---- second layer: h2 = b2 + W2^T relu(h1)
+      uint64_t h2[E][16];
+      {
+        const ulonglong2* brow = reinterpret_cast<const ulonglong2*>(&sm.w[L::B2]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const ulonglong2 b = brow[j];
+#pragma unroll
+          for (int e = 0; e < E; ++e) { h2[e][2 * j] = b.x; h2[e][2 * j + 1] = b.y; }
+        }
+      }
+#pragma unroll 2
+      for (int k = 0; k < 32; ++k) {
+        uint64_t hk[E];
+        if constexpr (E == 4) {
+          const float4 a = ld4(&sm.h1[k][tid][0]);
+          hk[0] = pack2(a.x, a.x); hk[1] = pack2(a.y, a.y); hk[E - 2] = pack2(a.z, a.z); hk[E - 1] = pack2(a.w, a.w);
+        } else {
+          const float2 a = *reinterpret_cast<const float2*>(&sm.h1[k][tid][0]);
+          hk[0] = pack2(a.x, a.x); hk[1] = pack2(a.y, a.y);
+        }
+        const ulonglong2* wrow = reinterpret_cast<const ulonglong2*>(&sm.w[L::W2 + k * 32]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const ulonglong2 w = wrow[j];
+#pragma unroll
+          for (int e = 0; e < E; ++e) {
+            h2[e][2 * j] = fma2(w.x, hk[e], h2[e][2 * j]);
+            h2[e][2 * j + 1] = fma2(w.y, hk[e], h2[e][2 * j + 1]);
+          }
+        }
+      }
+      // ---- output layer: (direction, magnitude) as one packed accumulator per row
+      const uint64_t b3 = *reinterpret_cast<const uint64_t*>(&sm.w[L::B3]);
+      uint64_t out[E];
+#pragma unroll
+      for (int e = 0; e < E; ++e) out[e] = b3;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(&sm.w[L::W3 + 4 * j]);  // rows 2j and 2j+1
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          float a, b;
+          unpack2(h2[e][j], a, b);
+          a = fmaxf(a, 0.f); b = fmaxf(b, 0.f);
+          out[e] = fma2(w.x, pack2(a, a), out[e]);
+          out[e] = fma2(w.y, pack2(b, b), out[e]);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const int x = x0 + rg + ng * (q + e);
+        if (colok && x < X) {
+          float o0, o1;
+          unpack2(out[e], o0, o1);
+          pp[(int64_t)x * Y + y] = finish<PYLO_FAM_ADAFAC>(cp[e], o0, o1, d, 1.0f, lr_eff, prm.wd_mode);
+        }
+      }
+      if (more) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) { cg[e] = ng_[e]; cp[e] = np_[e]; cm0[e] = nm0[e]; cm1[e] = nm1[e]; cm2[e] = nm2[e]; cv[e] = nv[e]; }
       }
     }
   }
@@ -1157,6 +1393,20 @@ int pylo_b200_apply(const pylo_tensor_desc* descs, const pylo_tile* tiles, int n
     case PYLO_FAM_VELO: k_apply<PYLO_FAM_VELO><<<grid_for(n_tiles, 4), NT, 0, s>>>(descs, tiles, n_tiles, reverse, *prm); break;
     default: return -2;
   }
+  return launch_status();
+}
+
+int pylo_b200_apply_adafac_cols(const pylo_tensor_desc* descs, const pylo_atile* ctiles, int n_ctiles,
+                                const pylo_step_params* prm, void* stream) {
+  CHECK_ARG(descs && ctiles && prm && n_ctiles >= 0 && prm->family == PYLO_FAM_ADAFAC);
+  if (n_ctiles == 0) return 0;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(k_apply_adafac_cols, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(CcSmem));
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  k_apply_adafac_cols<<<grid_for(n_ctiles, CC_CTAS_PER_SM), NT, sizeof(CcSmem), (cudaStream_t)stream>>>(descs, ctiles, n_ctiles, *prm);
   return launch_status();
 }
 

@@ -238,6 +238,24 @@ class LoPlan:
         self.n_units = U
         self.total_elems = int(sum(sizes))
         self._keepalive = []
+        # AdafacLO / ELO: FAST2D tensors take the thread-owns-column apply kernel, the rest the generic one
+        self.ctiles = None
+        if family == L.FAM_ADAFAC:
+            ctiles = []
+            for i in range(T):
+                if tdesc["mode"][i] != L.MODE_FAST2D:
+                    continue
+                X, Y = int(tdesc["X"][i]), int(tdesc["Y"][i])
+                cw = min((256, 128, 64, 32), key=lambda c: ((Y + c - 1) // c * c - Y, -c))
+                rt = 16 if cw == 256 else 32
+                for rtile in range((X + rt - 1) // rt):
+                    for ctile in range((Y + cw - 1) // cw):
+                        ctiles.append((i, rtile, ctile, cw))
+            self.ctiles = DeviceTable(np.array(ctiles, dtype=np.int32).reshape(-1, 4).view(L.ATILE_DTYPE).reshape(-1), self.device)
+            self.n_ctiles = len(ctiles)
+            slow = np.array([t for t in tiles if udesc["mode"][t["tensor"]] != L.MODE_FAST2D], dtype=L.TILE_DTYPE)
+            self.tiles_slow = DeviceTable(slow, self.device)
+            self.n_tiles_slow = len(slow)
 
     # ------------------------------------------------------------------ per-step refresh
     def set_field(self, name, values):
@@ -267,7 +285,7 @@ class LoPlan:
     # ------------------------------------------------------------------ launch sequence
     #: kernels each C-ABI call launches (for the launch count the benchmark reports)
     LAUNCHES = {"rowcol_sums": 1, "factor_update": 1, "state_moments": 1, "finalize_moments": 1,
-                "prep_apply": 1, "apply": 1}
+                "prep_apply": 1, "apply": 1, "apply_cols": 1}
 
     def enable_profile(self, on: bool = True):
         """Record a CUDA-event pair around every phase launch (read back with :meth:`phase_times`)."""
@@ -305,7 +323,13 @@ class LoPlan:
         """Phases P, C."""
         pp = C.byref(prm)
         self._call("prep_apply", L.lib.pylo_b200_prep_apply, self.desc.ptr, self.n_units, pp, stream)
-        self._call("apply", L.lib.pylo_b200_apply, self.desc.ptr, self.tiles.ptr, self.n_tiles, int(reverse_c), pp, stream)
+        if self.ctiles is not None:
+            if self.n_ctiles:
+                self._call("apply_cols", L.lib.pylo_b200_apply_adafac_cols, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp, stream)
+            if self.n_tiles_slow:
+                self._call("apply", L.lib.pylo_b200_apply, self.desc.ptr, self.tiles_slow.ptr, self.n_tiles_slow, int(reverse_c), pp, stream)
+        else:
+            self._call("apply", L.lib.pylo_b200_apply, self.desc.ptr, self.tiles.ptr, self.n_tiles, int(reverse_c), pp, stream)
 
 
 class GradNorm:
