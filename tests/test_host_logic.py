@@ -1,0 +1,92 @@
+"""Host-side logic that needs no GPU: factored-dims rules, geometry, tiling, ownership, flat layout."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import pylo_oracle as O
+from pylo_b200 import _lib as L
+from pylo_b200 import plan, workloads, zero
+from pylo_b200.optim import _common as K
+
+SHAPES = [(64, 32), (32, 64), (48, 48), (7, 5, 3), (12, 3, 4, 4), (4, 4, 9, 9), (768, 3, 16, 16), (5,), ()]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_factored_dims_rules_agree_with_the_oracle(shape):
+    assert K.factored_dims_sorted(shape) == O.factored_dims_sorted(shape)
+    assert K.factored_dims_argsort(shape) == O.factored_dims_argsort(shape)
+    assert K.factored_dims_velo(shape) == O.factored_dims_velo(shape)
+
+
+def test_velo_tie_rule():
+    assert K.factored_dims_velo((1024, 1024)) == (1, 0)       # equal sizes swap (velo_cuda.py:121-131)
+    assert K.factored_dims_velo((8, 8, 3, 3)) == (0, 1)       # except 4-D with axes (0, 1)
+    assert K.factored_dims_sorted((4096, 4096)) == (0, 1)
+
+
+@pytest.mark.parametrize("shape", [s for s in SHAPES if len(s) >= 2])
+def test_geometry_indexes_like_broadcasting(shape):
+    """a / b vector indices from the 5-D view equal what broadcasting a keep-dim vector would read."""
+    fd = K.factored_dims_argsort(shape)
+    dc, dr = fd
+    Ov, X, M, Y, I, r_is_a = plan.geometry(shape, fd)
+    n = int(np.prod(shape))
+    idx = np.arange(n)
+    i = idx % I; t = idx // I; y = t % Y; t //= Y; m = t % M; t //= M; x = t % X; o = t // X
+    a = ((o * X + x) * M + m) * I + i
+    b = ((o * M + m) * Y + y) * I + i
+    r_shape, c_shape = list(shape), list(shape)
+    r_shape[dr], c_shape[dc] = 1, 1
+    rvec = np.arange(int(np.prod(r_shape))).reshape(r_shape)
+    cvec = np.arange(int(np.prod(c_shape))).reshape(c_shape)
+    r_b = np.broadcast_to(rvec, shape).reshape(-1)
+    c_b = np.broadcast_to(cvec, shape).reshape(-1)
+    assert np.array_equal(r_b, a if r_is_a else b)
+    assert np.array_equal(c_b, b if r_is_a else a)
+
+
+def test_tiles_cover_every_element_once():
+    sizes = [1, L.TILE_ELEMS, L.TILE_ELEMS + 1, 5 * L.TILE_ELEMS - 3]
+    tiles, ranges = plan.make_tiles(sizes)
+    for i, n in enumerate(sizes):
+        t0, k = ranges[i]
+        mine = tiles[t0:t0 + k]
+        assert (mine["tensor"] == i).all()
+        assert mine["start"][0] == 0 and (np.diff(mine["start"]) == L.TILE_ELEMS).all()
+        assert mine["start"][-1] < n <= mine["start"][-1] + L.TILE_ELEMS
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_partition_is_deterministic_balanced_and_total(world):
+    shapes = workloads.llama3_8b()
+    owner = zero.partition(shapes, world)
+    assert owner == zero.partition(shapes, world)
+    loads = [sum(workloads.numel(s) for s, o in zip(shapes, owner) if o == r) for r in range(world)]
+    assert sum(loads) == workloads.total_params(shapes)
+    assert max(loads) / (sum(loads) / world) < 1.01
+    offsets, shard = zero.flat_layout(shapes, owner, world)
+    spans = sorted((off, off + workloads.numel(s)) for off, s in zip(offsets, shapes))
+    assert all(a1 <= b0 for (_, a1), (b0, _) in zip(spans, spans[1:])), "tensors overlap in the flat buffer"
+    assert all(off % zero.ALIGN == 0 for off in offsets)
+    assert all(o * shard <= off < (o + 1) * shard for off, o in zip(offsets, owner))
+
+
+def test_workload_sizes():
+    assert workloads.total_params(workloads.mlp_784()) == 118282
+    assert workloads.total_params(workloads.celo2_4096()) == 4096 * 4096 + 4096
+    assert abs(workloads.total_params(workloads.llama3_8b()) - 8.03e9) < 1e7
+    assert abs(workloads.total_params(workloads.gpt2_medium()) - 354.8e6) < 1e6
+    assert abs(workloads.total_params(workloads.vit_b16()) - 86.6e6) < 1e6
+
+
+def test_cuda_classes_refuse_to_run_without_a_gpu():
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    from pylo_b200 import models, optim
+
+    p = [torch.nn.Parameter(torch.zeros(4, 4))]
+    with pytest.raises(RuntimeError):
+        optim.CELO2_CUDA(p, network=models.CELO2MLP())
+    with pytest.raises(RuntimeError):
+        optim.AdafacLO_CUDA(p, network=models.MetaMLP(39, 32, 1))
