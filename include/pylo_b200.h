@@ -151,6 +151,31 @@ typedef struct pylo_gvec {
 int pylo_b200_grad_sumsq(const pylo_gvec* items, const pylo_tile* tiles, int n_tiles,
                          float* scratch, float* out, void* stream);
 
+/* The same sum of squares for callers that cannot provide scratch memory (no counterpart in the
+ * reference: it never needs scratch because it reduces with atomics).
+ *
+ * Who needs it: a host that cannot allocate device memory for us - for example a binding from another
+ * language that links nothing but this library, or an optimizer hook that is forbidden to call
+ * cudaMalloc inside the step because cudaMalloc stalls the whole device.  This entry point calls no
+ * cudaMalloc / cudaFree and no allocating library routine; the per-tile partial sums go to a fixed
+ * array inside the library (PYLO_STATIC_SCRATCH_TILES floats = 256 KiB, resident on every GPU that
+ * loads the library until the process ends).
+ *
+ * Limits and rules:
+ *  - n_tiles <= PYLO_STATIC_SCRATCH_TILES (2^16 tiles = 2^30 gradient elements); more is refused with
+ *    PYLO_ERR_STATIC_SCRATCH_TOO_SMALL and nothing is launched.
+ *  - The first call on each device looks up the array's device address (with that device current).
+ *    Make that first call during set-up, before any stream capture begins.
+ *  - All calls share the one array, and it keeps whatever the previous call left in it.  That is
+ *    harmless here (each call overwrites every slot it later reads, so nothing needs zeroing), but two
+ *    calls that overlap on the GPU - different streams, or different host threads - race on it and
+ *    give wrong sums.  Serialise them.
+ * items, tiles, out, stream: as for pylo_b200_grad_sumsq. */
+#define PYLO_STATIC_SCRATCH_TILES 65536
+#define PYLO_ERR_STATIC_SCRATCH_TOO_SMALL (-4)
+int pylo_b200_grad_sumsq_static(const pylo_gvec* items, const pylo_tile* tiles, int n_tiles, float* out,
+                                void* stream);
+
 /* Phase A: row and column sums of g'^2 + 1e-30 (the reductions inside
  * grad_sqr.mean(dim=dr / dc), AdafacLO_cuda.py:333-340, CELO2_cuda.py:218-224, velo_cuda.py:531-541).
  * atiles cover the FAST2D tensors; generic_ids lists the GENERIC tensors. */

@@ -84,6 +84,7 @@ def _load():
         "pylo_b200_sizeof_desc": [],
         "pylo_b200_sizeof_params": [],
         "pylo_b200_grad_sumsq": [vp, vp, i32, vp, vp, vp],
+        "pylo_b200_grad_sumsq_static": [vp, vp, i32, vp, vp],
         "pylo_b200_rowcol_sums": [vp, vp, i32, vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_factor_update": [vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_state_moments": [vp, vp, i32, i32, C.POINTER(StepParams), vp],
@@ -112,8 +113,15 @@ def _load():
 lib, EXPORTED = _load()
 
 
+STATIC_SCRATCH_TILES = 65536
+ERR_STATIC_SCRATCH_TOO_SMALL = -4
+
+
 def check(code, what):
     """Turn a non-zero return code of the C ABI into an exception."""
+    if code == ERR_STATIC_SCRATCH_TOO_SMALL:
+        raise PyloLibError(f"{what}: more than {STATIC_SCRATCH_TILES} tiles ({STATIC_SCRATCH_TILES * TILE_ELEMS} "
+                           "elements) do not fit the library's built-in scratch array; pass a scratch buffer instead")
     if code != 0:
         kind = "argument rejected" if code < 0 else "CUDA error"
         raise PyloLibError(f"{what}: {kind} (code {code})")

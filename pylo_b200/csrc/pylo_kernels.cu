@@ -8,6 +8,8 @@
 // All reductions go through fixed-slot partials and fixed-order final sums, so
 // results are bit-reproducible from run to run (no floating-point atomics).
 
+#include <mutex>
+
 #include "pylo_common.cuh"
 
 // ================================================================================================
@@ -1314,6 +1316,57 @@ int pylo_b200_grad_sumsq(const pylo_gvec* descs, const pylo_tile* tiles, int n_t
   CHECK_ARG(descs && tiles && scratch && out && n_tiles >= 0);
   cudaStream_t s = (cudaStream_t)stream;
   if (n_tiles > 0) k_grad_sumsq<<<grid_for(n_tiles, 8), NT, 0, s>>>(descs, tiles, n_tiles, scratch);
+  k_sum_final<<<1, 1024, 0, s>>>(scratch, n_tiles, out);
+  return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of pylo_b200_grad_sumsq.
+//
+// Some hosts of this library cannot hand it scratch memory: a language binding that links only this
+// .so and has no device allocator of its own, or a step loop whose rules forbid cudaMalloc because it
+// synchronises the device.  For them the per-tile partial sums live in the fixed array below instead
+// of a caller buffer.  The array is part of the loaded module, so every GPU that loads the library
+// carries its 256 KiB until the process exits.
+//
+// In host code the name `g_static_sumsq_scratch` is only a handle for the symbol, not a pointer the
+// device can follow, so the device address is looked up with cudaGetSymbolAddress, once per device,
+// with that device current, and that address is what the kernels receive.
+// ------------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_static_sumsq_scratch[PYLO_STATIC_SCRATCH_TILES];
+
+#define PYLO_MAX_DEVICES 64
+static float* g_static_scratch_addr[PYLO_MAX_DEVICES] = {nullptr};
+static std::mutex g_static_scratch_mutex;
+
+static int static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= PYLO_MAX_DEVICES) return -3;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_static_sumsq_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (p == nullptr) return -3;
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return 0;
+}
+
+int pylo_b200_grad_sumsq_static(const pylo_gvec* items, const pylo_tile* tiles, int n_tiles, float* out,
+                                void* stream) {
+  CHECK_ARG(items && tiles && out && n_tiles >= 0);
+  if (n_tiles > PYLO_STATIC_SCRATCH_TILES) return PYLO_ERR_STATIC_SCRATCH_TOO_SMALL;
+  float* scratch = nullptr;
+  const int rc = static_scratch_for_current_device(&scratch);
+  if (rc != 0) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  // every slot that the final sum reads is written by the partial kernel of this same call, so
+  // nothing left over from an earlier call needs clearing
+  if (n_tiles > 0) k_grad_sumsq<<<grid_for(n_tiles, 8), NT, 0, s>>>(items, tiles, n_tiles, scratch);
   k_sum_final<<<1, 1024, 0, s>>>(scratch, n_tiles, out);
   return launch_status();
 }
