@@ -77,8 +77,8 @@ typedef struct pylo_tensor_desc {
   float* sum_b;   /* workspace [Lb]: sum over X */
   float* part_a;  /* workspace [X][n_cb]  row-sum partials (FAST2D) */
   float* part_b;  /* workspace [n_strips][Y] column-sum partials (FAST2D) */
-  float* h_a;     /* workspace [La][H]: first-layer contribution of the "a" features (+ bias) */
-  float* h_b;     /* workspace [Lb][H] */
+  float* h_a;     /* workspace [La][H] (ADAFAC) or [La][H][2] (CELO2, VELO): first-layer term of the "a" features (+ bias) */
+  float* h_b;     /* workspace [H][Lb]: first-layer term of the "b" features */
   float* closed;  /* workspace [PYLO_STAT_STRIDE]: closed-form sums of squares of vector features */
   float* sums;    /* workspace [PYLO_STAT_STRIDE]: per-tensor sums (features, then VeLO statistics) */
   float* wfold;   /* workspace [PYLO_WFOLD_STRIDE]: network with normalisers folded in */
@@ -178,10 +178,12 @@ int pylo_b200_grad_sumsq_static(const pylo_gvec* items, const pylo_tile* tiles, 
 
 /* Phase A: row and column sums of g'^2 + 1e-30 (the reductions inside
  * grad_sqr.mean(dim=dr / dc), AdafacLO_cuda.py:333-340, CELO2_cuda.py:218-224, velo_cuda.py:531-541).
- * atiles cover the FAST2D tensors; generic_ids lists the GENERIC tensors. */
+ * atiles cover the FAST2D tensors (strip x 1024-column block each; they leave per-strip column partials);
+ * rtiles, one per (FAST2D tensor, 1024-column block), drive the second-level sum of those partials over the
+ * strips; generic_ids lists the GENERIC tensors. */
 int pylo_b200_rowcol_sums(const pylo_tensor_desc* descs, const pylo_atile* atiles, int n_atiles,
-                          const int32_t* generic_ids, int n_generic, const pylo_step_params* prm,
-                          void* stream);
+                          const pylo_atile* rtiles, int n_rtiles, const int32_t* generic_ids, int n_generic,
+                          const pylo_step_params* prm, void* stream);
 
 /* Phase A2, one CTA per tensor: EMA of the factored accumulators, row_col_mean,
  * row/column rsqrt factors (AdafacLO_cuda.py:342-345, CELO2_cuda.py:229-231, velo_cuda.py:716-729)
@@ -219,9 +221,17 @@ int pylo_b200_apply(const pylo_tensor_desc* descs, const pylo_tile* tiles, int n
  * the FMA-bound 39-32-32-2 network: a thread keeps one column, packed fp32x2 FMAs).  ctiles: one entry per
  * tile with strip = row-tile index, cb = column-tile index, pad_ = columns per CTA (32, 64, 128 or 256); a tile
  * has 16 rows at 256 columns and 32 rows otherwise.  With this kernel in use pylo_b200_apply gets only the non-FAST2D tiles.
- * For this family pylo_b200_prep_apply stores desc.h_b transposed, [32][Y]. */
+ * With one of the FAST2D kernels in use pylo_b200_apply handles the GENERIC and VEC1D units only. */
 int pylo_b200_apply_adafac_cols(const pylo_tensor_desc* descs, const pylo_atile* ctiles, int n_ctiles,
                                 const pylo_step_params* prm, void* stream);
+
+/* Phase C for the FAST2D tensors of the CELO2 and VELO families (same arithmetic as pylo_b200_apply, done on
+ * pairs of adjacent elements with packed fp32x2 instructions).  ctiles: strip = row-tile index, cb = column-tile
+ * index, pad_ = threads per row (8 .. 256, a thread owns 4 columns); a tile has 8 * (256 / pad_) rows and
+ * 4 * pad_ columns.  For these families pylo_b200_prep_apply stores desc.h_a as (v, v) pairs, [X][H][2], and
+ * for every family desc.h_b transposed, [H][Y]. */
+int pylo_b200_apply_packed(const pylo_tensor_desc* descs, const pylo_atile* ctiles, int n_ctiles,
+                           const pylo_step_params* prm, void* stream);
 
 /* CELO2 tail (CELO2_cuda.py:336-339): step * rsqrt(mean(step^2 over the last two axes) + 1e-9) * rmsmult,
  * then p -= lr * (step + wd * p).  Items are matrices (the last two axes of a tensor). */

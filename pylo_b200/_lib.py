@@ -85,13 +85,14 @@ def _load():
         "pylo_b200_sizeof_params": [],
         "pylo_b200_grad_sumsq": [vp, vp, i32, vp, vp, vp],
         "pylo_b200_grad_sumsq_static": [vp, vp, i32, vp, vp],
-        "pylo_b200_rowcol_sums": [vp, vp, i32, vp, i32, C.POINTER(StepParams), vp],
+        "pylo_b200_rowcol_sums": [vp, vp, i32, vp, i32, vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_factor_update": [vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_state_moments": [vp, vp, i32, i32, C.POINTER(StepParams), vp],
         "pylo_b200_finalize_moments": [vp, i32, vp],
         "pylo_b200_prep_apply": [vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_apply": [vp, vp, i32, i32, C.POINTER(StepParams), vp],
         "pylo_b200_apply_adafac_cols": [vp, vp, i32, C.POINTER(StepParams), vp],
+        "pylo_b200_apply_packed": [vp, vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_celo2_post_sums": [vp, vp, i32, vp],
         "pylo_b200_celo2_post_apply": [vp, vp, i32, vp],
         "pylo_b200_adamw": [vp, vp, i32, i32, f32, f32, f32, f32, f32, C.POINTER(StepParams), vp],

@@ -142,6 +142,33 @@ __global__ void __launch_bounds__(NT) k_rowcol_fast(const pylo_tensor_desc* __re
   }
 }
 
+// Second level of the column sums: sum_b[y] = sum over strips of part_b[strip][y], strips in order.
+// One work item = 1024 columns of one tensor; a thread owns a float4 of columns.
+__global__ void __launch_bounds__(NT) k_colpart_reduce(const pylo_tensor_desc* __restrict__ descs,
+                                                       const pylo_atile* __restrict__ rtiles, int n_rtiles) {
+  for (int t = blockIdx.x; t < n_rtiles; t += gridDim.x) {
+    const pylo_atile rt = rtiles[t];
+    const pylo_tensor_desc& d = descs[rt.tensor];
+    const int Y = d.Y, strips = d.n_strips;
+    const int y = rt.cb * PYLO_A_COLS + threadIdx.x * 4;
+    if (y >= Y) continue;
+    const float* __restrict__ src = d.part_b + y;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    int r = 0;
+    for (; r + 4 <= strips; r += 4) {  // four loads in flight, added in strip order
+      const float4 q0 = ld4(src + (int64_t)r * Y), q1 = ld4(src + (int64_t)(r + 1) * Y);
+      const float4 q2 = ld4(src + (int64_t)(r + 2) * Y), q3 = ld4(src + (int64_t)(r + 3) * Y);
+      acc.x = (((acc.x + q0.x) + q1.x) + q2.x) + q3.x; acc.y = (((acc.y + q0.y) + q1.y) + q2.y) + q3.y;
+      acc.z = (((acc.z + q0.z) + q1.z) + q2.z) + q3.z; acc.w = (((acc.w + q0.w) + q1.w) + q2.w) + q3.w;
+    }
+    for (; r < strips; ++r) {
+      const float4 q = ld4(src + (int64_t)r * Y);
+      acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+    }
+    st4(d.sum_b + y, acc);
+  }
+}
+
 // GENERIC tensors: one warp per output vector element, lanes stride over the reduced axis.
 __global__ void __launch_bounds__(NT) k_rowcol_generic(const pylo_tensor_desc* __restrict__ descs,
                                                        const int32_t* __restrict__ ids, int slices,
@@ -207,11 +234,7 @@ __global__ void __launch_bounds__(A2_NT) k_factor_update(const pylo_tensor_desc*
       for (int c = 0; c < d.n_cb; ++c) s += d.part_a[x * d.n_cb + c];
       d.sum_a[x] = s;
     }
-    for (int64_t y = tid; y < Y; y += A2_NT) {
-      float s = 0.f;
-      for (int r = 0; r < d.n_strips; ++r) s += d.part_b[(int64_t)r * Y + y];
-      d.sum_b[y] = s;
-    }
+    // the column sums were finished by k_colpart_reduce
   }
   __syncthreads();
 
@@ -553,7 +576,8 @@ __global__ void __launch_bounds__(NT) k_prep_apply(const pylo_tensor_desc* __res
       acc = fmaf(s_w1[(ka + k) * H + j], r, acc);
       acc = fmaf(s_w1[(kra + k) * H + j], rsqrtf(r + 1e-8f), acc);
     }
-    d.h_a[e] = acc;
+    if (FAM == PYLO_FAM_ADAFAC) d.h_a[e] = acc;
+    else { d.h_a[2 * e] = acc; d.h_a[2 * e + 1] = acc; }  // stored as (v, v) pairs for the packed kernel
   }
   for (int64_t e = (int64_t)slice * NT + tid; e < Lb * H; e += (int64_t)slices * NT) {
     const int64_t i = e / H;
@@ -565,8 +589,7 @@ __global__ void __launch_bounds__(NT) k_prep_apply(const pylo_tensor_desc* __res
       acc = fmaf(s_w1[(kb + k) * H + j], r, acc);
       acc = fmaf(s_w1[(krb + k) * H + j], rsqrtf(r + 1e-8f), acc);
     }
-    if (FAM == PYLO_FAM_ADAFAC) d.h_b[(int64_t)j * Lb + i] = acc;  // transposed for the column kernel
-    else d.h_b[e] = acc;
+    d.h_b[(int64_t)j * Lb + i] = acc;  // transposed, [H][Y]: a thread reads its columns' terms with one float4
   }
 }
 
@@ -633,20 +656,28 @@ __device__ __forceinline__ void network(const uint32_t s_w, float (&h1)[E][Fam<F
   });
 }
 
+// per-tensor scalars of the output stage, read once per tile
+struct Fin {
+  float exp_mult, step_mult, wd, lr, lr_eff, param_scale;
+  int wd_mode;
+};
+__device__ __forceinline__ Fin make_fin(const pylo_tensor_desc& d, float param_scale, float lr_eff, int wd_mode) {
+  return Fin{d.exp_mult, d.step_mult, d.wd, d.lr, lr_eff, param_scale, wd_mode};
+}
+
 template <int FAM>
-__device__ __forceinline__ float finish(float p, float o0, float o1, const pylo_tensor_desc& d, float param_scale,
-                                        float lr_eff, int wd_mode) {
-  if (FAM == PYLO_FAM_CELO2) return o0 * __expf(o1 * d.exp_mult);
+__device__ __forceinline__ float finish(float p, float o0, float o1, const Fin& c) {
+  if (FAM == PYLO_FAM_CELO2) return o0 * __expf(o1 * c.exp_mult);
   if (FAM == PYLO_FAM_ADAFAC) {
-    const float upd = o0 * __expf(o1 * d.exp_mult) * d.step_mult;
-    float pn = p - lr_eff * upd;
-    if (wd_mode == 1) pn = fmaf(-(d.wd * d.lr), pn, pn);
-    else if (wd_mode == 2) pn = fmaf(-(d.wd * d.lr), p, pn);
+    const float upd = o0 * __expf(o1 * c.exp_mult) * c.step_mult;
+    float pn = p - c.lr_eff * upd;
+    if (c.wd_mode == 1) pn = fmaf(-(c.wd * c.lr), pn, pn);
+    else if (c.wd_mode == 2) pn = fmaf(-(c.wd * c.lr), p, pn);
     return pn;
   }
-  const float upd = param_scale * o0 * __expf(o1 * d.exp_mult) * d.step_mult;
-  float pn = p - lr_eff * upd;
-  if (d.wd > 0.f) pn = pn - d.wd * lr_eff * pn;
+  const float upd = c.param_scale * o0 * __expf(o1 * c.exp_mult) * c.step_mult;
+  float pn = p - c.lr_eff * upd;
+  if (c.wd > 0.f) pn = pn - c.wd * c.lr_eff * pn;
   return pn;
 }
 
@@ -674,7 +705,7 @@ __global__ void __launch_bounds__(NT) k_apply(const pylo_tensor_desc* __restrict
     const int64_t n = d.n, start = tl.start;
     const int cnt = (int)min((int64_t)PYLO_TILE_ELEMS, n - start);
     const float gs = grad_scale_of(d, prm);
-    const float param_scale = s_w[L::SC], lr_eff = s_w[L::SC + 1];
+    const Fin fin = make_fin(d, s_w[L::SC], s_w[L::SC + 1], prm.wd_mode);
     const float* gp = d.g + start;
     float* pp = d.p + start;
     float* op = (FAM == PYLO_FAM_CELO2) ? d.out + start : pp;
@@ -683,57 +714,7 @@ __global__ void __launch_bounds__(NT) k_apply(const pylo_tensor_desc* __restrict
     const float* m2p = d.m + 2 * d.m_stride + start;
     const float* vp = d.v + start;
 
-    if (d.mode == PYLO_MODE_FAST2D) {
-      const uint32_t Y = d.Y;
-      const bool small = n < (1ll << 32);
-      const float* __restrict__ fxp = d.fx;
-      const float* __restrict__ fbp = d.f_b;
-      const float* __restrict__ h_a = d.h_a;
-      const float* __restrict__ h_b = d.h_b;
-      for (int i = tid * 4; i < cnt; i += NT * 4) {
-        const int64_t idx = start + i;
-        uint32_t x, y;
-        if (small) { x = (uint32_t)idx / Y; y = (uint32_t)idx - x * Y; }
-        else { x = (uint32_t)(idx / Y); y = (uint32_t)(idx - (int64_t)x * Y); }
-        const float4 g4 = ldg4(gp + i), p4 = ld4(pp + i);
-        const float4 a0 = ld4(m0p + i), a1 = ld4(m1p + i), a2 = ld4(m2p + i), v4 = ld4(vp + i);
-        const float4 fa = ld4(fxp + 4 * (int64_t)x);
-        const float4 b0 = ld4(fbp + y), b1 = ld4(fbp + Y + y), b2 = ld4(fbp + 2 * (int64_t)Y + y);
-        // two pairs of elements; after each pair the upper halves rotate down so that all
-        // register indexing stays static
-        float ge[4] = {g4.x, g4.y, g4.z, g4.w}, pe[4] = {p4.x, p4.y, p4.z, p4.w};
-        float m0e[4] = {a0.x, a0.y, a0.z, a0.w}, m1e[4] = {a1.x, a1.y, a1.z, a1.w}, m2e[4] = {a2.x, a2.y, a2.z, a2.w};
-        float ve[4] = {v4.x, v4.y, v4.z, v4.w};
-        float b0e[4] = {b0.x, b0.y, b0.z, b0.w}, b1e[4] = {b1.x, b1.y, b1.z, b1.w}, b2e[4] = {b2.x, b2.y, b2.z, b2.w};
-        const float* ha = h_a + (int64_t)x * H;
-        const float* hb = h_b + (int64_t)y * H;
-        float res[4];
-#pragma unroll 1
-        for (int pr = 0; pr < 2; ++pr) {
-          float f[2][F::NF], h1[2][H], o0[2], o1[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const float g = xform_grad(ge[u], gs, prm.clip_val, prm.nan_to_num);
-            const float rs = rsqrtf(ve[u] + prm.eps_feat);
-            elem_features<FAM>(f[u], g, pe[u], m0e[u], m1e[u], m2e[u], ve[u], rs, fa.x * b0e[u], fa.y * b1e[u], fa.z * b2e[u]);
-#pragma unroll
-            for (int j = 0; j < H; j += 4) {
-              const float4 qa = ld4(ha + j), qb = ld4(hb + (pr * 2 + u) * H + j);
-              h1[u][j] = qa.x + qb.x; h1[u][j + 1] = qa.y + qb.y; h1[u][j + 2] = qa.z + qb.z; h1[u][j + 3] = qa.w + qb.w;
-            }
-          }
-          network<FAM, false, 2>(s_wa, h1, f, o0, o1);
-          const float r0 = finish<FAM>(pe[0], o0[0], o1[0], d, param_scale, lr_eff, prm.wd_mode);
-          const float r1 = finish<FAM>(pe[1], o0[1], o1[1], d, param_scale, lr_eff, prm.wd_mode);
-          res[0] = res[2]; res[1] = res[3]; res[2] = r0; res[3] = r1;
-          ge[0] = ge[2]; ge[1] = ge[3]; pe[0] = pe[2]; pe[1] = pe[3];
-          m0e[0] = m0e[2]; m0e[1] = m0e[3]; m1e[0] = m1e[2]; m1e[1] = m1e[3]; m2e[0] = m2e[2]; m2e[1] = m2e[3];
-          ve[0] = ve[2]; ve[1] = ve[3];
-          b0e[0] = b0e[2]; b0e[1] = b0e[3]; b1e[0] = b1e[2]; b1e[1] = b1e[3]; b2e[0] = b2e[2]; b2e[1] = b2e[3];
-        }
-        st4(op + i, make_float4(res[0], res[1], res[2], res[3]));
-      }
-    } else {
+    {
       const Geo geo{(uint32_t)d.X, (uint32_t)d.M, (uint32_t)d.Y, (uint32_t)d.I};
       const bool vec1d = d.mode == PYLO_MODE_VEC1D;
       const int64_t La = vec1d ? n : d.La, Lb = vec1d ? n : d.Lb;
@@ -763,7 +744,7 @@ __global__ void __launch_bounds__(NT) k_apply(const pylo_tensor_desc* __restrict
 #pragma unroll
         for (int j = 0; j < H; ++j) h1[0][j] = s_w[L::B1 + j];
         network<FAM, true, 1>(s_wa, h1, f, o0, o1);
-        op[i] = finish<FAM>(p, o0[0], o1[0], d, param_scale, lr_eff, prm.wd_mode);
+        op[i] = finish<FAM>(p, o0[0], o1[0], fin);
       }
     }
   }
@@ -797,6 +778,11 @@ __device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
 __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   uint64_t d;
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
 __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
@@ -861,7 +847,7 @@ __global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const 
     __syncthreads();
     const float fb0 = d.f_b[yc], fb1 = d.f_b[Y + yc], fb2 = d.f_b[2 * (int64_t)Y + yc];
     const float gs = grad_scale_of(d, prm);
-    const float lr_eff = sm.w[L::SC + 1];
+    const Fin fin = make_fin(d, 1.0f, sm.w[L::SC + 1], prm.wd_mode);
     const int64_t n = d.n;
     const float* __restrict__ gp = d.g;
     float* __restrict__ pp = d.p;
@@ -993,13 +979,221 @@ __global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const 
         if (colok && x < X) {
           float o0, o1;
           unpack2(out[e], o0, o1);
-          pp[(int64_t)x * Y + y] = finish<PYLO_FAM_ADAFAC>(cp[e], o0, o1, d, 1.0f, lr_eff, prm.wd_mode);
+          pp[(int64_t)x * Y + y] = finish<PYLO_FAM_ADAFAC>(cp[e], o0, o1, fin);
         }
       }
       if (more) {
 #pragma unroll
         for (int e = 0; e < E; ++e) { cg[e] = ng_[e]; cp[e] = np_[e]; cm0[e] = nm0[e]; cm1[e] = nm1[e]; cm2[e] = nm2[e]; cv[e] = nv[e]; }
       }
+    }
+  }
+}
+
+// ================================================================================================
+// Phase C for CELO2 / ELO_CELO2 / VeLO on FAST2D tensors: packed kernel.
+//
+// These networks are small (30-8-8-3, 30-4-4-3), so the sweep should run at HBM speed; what stands
+// in the way is the instruction count per element.  This kernel halves it:
+//   * all arithmetic is done on PAIRS OF ADJACENT ELEMENTS with packed fp32x2 instructions: a
+//     float4 load already is two such pairs, so no register moves are needed to form them;
+//   * weights sit in shared memory as (w, w) pairs, one 128-bit read feeds four elements;
+//   * a thread keeps four columns for all rows of its tile, so the columns' tabulated first-layer
+//     terms and factors stay in registers; the rows' terms arrive as broadcast loads;
+//   * the next row's six float4 operands are requested before the current row is computed.
+// ================================================================================================
+template <int FAM>
+struct PkW {  // duplicated-weight layout in shared memory (floats)
+  static constexpr int H = Fam<FAM>::H;
+  static constexpr int W1 = 0;                   // [30][H] pairs
+  static constexpr int W2 = W1 + 30 * H * 2;     // [H][H] pairs, k-major
+  static constexpr int B2 = W2 + H * H * 2;      // [H] pairs
+  static constexpr int W3 = B2 + H * 2;          // [H][2] pairs
+  static constexpr int B3 = W3 + H * 4;          // [2] pairs
+  static constexpr int SIZE = B3 + 4;
+};
+
+struct PkBase {  // packed per-pair operands the features are made of
+  uint64_t g, cg, p, m0, m1, m2, v, rs, k0, k1, k2;
+};
+
+template <int K>
+__device__ __forceinline__ uint64_t pk_feature(const PkBase& b) {
+  if constexpr (K == 0) return b.g;
+  else if constexpr (K == 1) return b.cg;
+  else if constexpr (K == 2) return b.p;
+  else if constexpr (K == 3) return b.m0;
+  else if constexpr (K == 4) return b.m1;
+  else if constexpr (K == 5) return b.m2;
+  else if constexpr (K == 6) return b.v;
+  else if constexpr (K == 7) return mul2(b.m0, b.rs);
+  else if constexpr (K == 8) return mul2(b.m1, b.rs);
+  else if constexpr (K == 9) return mul2(b.m2, b.rs);
+  else if constexpr (K == 10) return b.rs;
+  else if constexpr (K == 11) return mul2(b.k0, b.g);
+  else if constexpr (K == 12) return mul2(b.k1, b.g);
+  else if constexpr (K == 13) return mul2(b.k2, b.g);
+  else if constexpr (K == 14) return mul2(b.g, b.rs);
+  else if constexpr (K == 27) return mul2(b.k0, b.m0);
+  else if constexpr (K == 28) return mul2(b.k1, b.m1);
+  else return mul2(b.k2, b.m2);
+}
+
+#define PK_ROWS 8  // rows per thread in a tile
+
+template <int FAM>
+__global__ void __launch_bounds__(NT, 2) k_apply_packed(const pylo_tensor_desc* __restrict__ descs,
+                                                        const pylo_atile* __restrict__ ctiles, int n_ctiles,
+                                                        const pylo_step_params prm) {
+  using F = Fam<FAM>;
+  using L = Fold<FAM>;
+  using W = PkW<FAM>;
+  constexpr int H = F::H;
+  __shared__ __align__(16) float s_w[W::SIZE];
+  __shared__ float s_sc[2];
+  const int tid = threadIdx.x;
+  int loaded = -1;
+  for (int t = blockIdx.x; t < n_ctiles; t += gridDim.x) {
+    const pylo_atile ct = ctiles[t];
+    const pylo_tensor_desc& d = descs[ct.tensor];
+    const int X = d.X, Y = d.Y;
+    const int tpr = ct.pad_;          // threads per row: 8 .. 256 (a thread owns 4 columns)
+    const int ng = NT / tpr;          // row groups
+    const int rt = PK_ROWS * ng;      // rows per tile
+    const int x0 = ct.strip * rt, y0 = ct.cb * tpr * 4;
+    if (loaded != ct.tensor) {
+      __syncthreads();
+      const float* __restrict__ wf = d.wfold;
+      for (int e = tid; e < 30 * H; e += NT) { const float w = wf[L::W1 + e]; s_w[W::W1 + 2 * e] = w; s_w[W::W1 + 2 * e + 1] = w; }
+      for (int e = tid; e < H * H; e += NT) { const float w = wf[L::W2 + e]; s_w[W::W2 + 2 * e] = w; s_w[W::W2 + 2 * e + 1] = w; }
+      for (int e = tid; e < H; e += NT) { const float w = wf[L::B2 + e]; s_w[W::B2 + 2 * e] = w; s_w[W::B2 + 2 * e + 1] = w; }
+      for (int e = tid; e < H * 2; e += NT) { const float w = wf[L::W3 + e]; s_w[W::W3 + 2 * e] = w; s_w[W::W3 + 2 * e + 1] = w; }
+      for (int e = tid; e < 2; e += NT) { const float w = wf[L::B3 + e]; s_w[W::B3 + 2 * e] = w; s_w[W::B3 + 2 * e + 1] = w; s_sc[e] = wf[L::SC + e]; }
+      loaded = ct.tensor;
+      __syncthreads();
+    }
+    const int y = y0 + 4 * (tid % tpr), rg = tid / tpr;
+    const bool colok = y < Y;
+    const int yc = colok ? y : 0;
+    const Fin fin = make_fin(d, s_sc[0], s_sc[1], prm.wd_mode);
+    const float gs = grad_scale_of(d, prm);
+    const float eps_feat = prm.eps_feat, clip = prm.clip_val;
+    const int64_t n = d.n;
+    // the four columns' first-layer terms and factors: pairs (col, col+1) and (col+2, col+3)
+    uint64_t hb[2][H], fb[2][3];
+#pragma unroll
+    for (int j = 0; j < H; ++j) {
+      const float4 q = ld4(d.h_b + (int64_t)j * Y + yc);
+      hb[0][j] = pack2(q.x, q.y);
+      hb[1][j] = pack2(q.z, q.w);
+    }
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+      const float4 q = ld4(d.f_b + (int64_t)k * Y + yc);
+      fb[0][k] = pack2(q.x, q.y);
+      fb[1][k] = pack2(q.z, q.w);
+    }
+    const float* __restrict__ gp = d.g;
+    float* __restrict__ pp = d.p;
+    float* __restrict__ op = (FAM == PYLO_FAM_CELO2) ? d.out : d.p;
+    const float* __restrict__ mp = d.m;
+    const float* __restrict__ vp = d.v;
+    const float* __restrict__ hap = d.h_a;
+    const float* __restrict__ fxp = d.fx;
+
+    float4 cg, cp, cm0, cm1, cm2, cv;
+    auto load_row = [&](int q, float4& g, float4& p, float4& m0, float4& m1, float4& m2, float4& v) {
+      const int x = x0 + rg + ng * q;
+      const int64_t idx = (colok && x < X) ? (int64_t)x * Y + y : 0;
+      g = ldg4(gp + idx); p = ld4(pp + idx); m0 = ld4(mp + idx); m1 = ld4(mp + n + idx); m2 = ld4(mp + 2 * n + idx); v = ld4(vp + idx);
+    };
+    load_row(0, cg, cp, cm0, cm1, cm2, cv);
+#pragma unroll 1
+    for (int q = 0; q < PK_ROWS; ++q) {
+      float4 ng_, np_, nm0, nm1, nm2, nv;
+      if (q + 1 < PK_ROWS) load_row(q + 1, ng_, np_, nm0, nm1, nm2, nv);
+      const int x = x0 + rg + ng * q;
+      const int xc = x < X ? x : 0;
+      const float4 fa = ld4(fxp + 4 * (int64_t)xc);
+      PkBase b[2];
+      {
+        float ge[4] = {cg.x, cg.y, cg.z, cg.w};
+        float rs[4] = {rsqrtf(cv.x + eps_feat), rsqrtf(cv.y + eps_feat), rsqrtf(cv.z + eps_feat), rsqrtf(cv.w + eps_feat)};
+        float cl[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { ge[u] = xform_grad(ge[u], gs, clip, prm.nan_to_num); cl[u] = fminf(fmaxf(ge[u], -0.1f), 0.1f); }
+        const uint64_t a0 = pack2(fa.x, fa.x), a1 = pack2(fa.y, fa.y), a2 = pack2(fa.z, fa.z);
+        b[0] = PkBase{pack2(ge[0], ge[1]), pack2(cl[0], cl[1]), pack2(cp.x, cp.y), pack2(cm0.x, cm0.y), pack2(cm1.x, cm1.y),
+                      pack2(cm2.x, cm2.y), pack2(cv.x, cv.y), pack2(rs[0], rs[1]), mul2(a0, fb[0][0]), mul2(a1, fb[0][1]), mul2(a2, fb[0][2])};
+        b[1] = PkBase{pack2(ge[2], ge[3]), pack2(cl[2], cl[3]), pack2(cp.z, cp.w), pack2(cm0.z, cm0.w), pack2(cm1.z, cm1.w),
+                      pack2(cm2.z, cm2.w), pack2(cv.z, cv.w), pack2(rs[2], rs[3]), mul2(a0, fb[1][0]), mul2(a1, fb[1][1]), mul2(a2, fb[1][2])};
+      }
+      // first layer: h1 = (row term + column term) + sum_k W1[k] f_k
+      uint64_t h1[2][H];
+#pragma unroll
+      for (int j = 0; j < H; j += 2) {
+        const ulonglong2 a = *reinterpret_cast<const ulonglong2*>(hap + ((int64_t)xc * H + j) * 2);
+        h1[0][j] = add2(hb[0][j], a.x); h1[0][j + 1] = add2(hb[0][j + 1], a.y);
+        h1[1][j] = add2(hb[1][j], a.x); h1[1][j + 1] = add2(hb[1][j + 1], a.y);
+      }
+      static_for<0, F::NF>([&](auto kc) {
+        constexpr int k = decltype(kc)::value;
+        if constexpr (!is_vec_feature<FAM>(k)) {
+          const uint64_t f0 = pk_feature<k>(b[0]), f1 = pk_feature<k>(b[1]);
+#pragma unroll
+          for (int j = 0; j < H; j += 2) {
+            const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(&s_w[W::W1 + (k * H + j) * 2]);
+            h1[0][j] = fma2(w.x, f0, h1[0][j]); h1[0][j + 1] = fma2(w.y, f0, h1[0][j + 1]);
+            h1[1][j] = fma2(w.x, f1, h1[1][j]); h1[1][j + 1] = fma2(w.y, f1, h1[1][j + 1]);
+          }
+        }
+      });
+      // second layer
+      uint64_t h2[2][H];
+#pragma unroll
+      for (int j = 0; j < H; j += 2) {
+        const ulonglong2 bb = *reinterpret_cast<const ulonglong2*>(&s_w[W::B2 + j * 2]);
+        h2[0][j] = bb.x; h2[0][j + 1] = bb.y; h2[1][j] = bb.x; h2[1][j + 1] = bb.y;
+      }
+      static_for<0, H>([&](auto kc) {
+        constexpr int k = decltype(kc)::value;
+        uint64_t r[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          float lo, hi;
+          unpack2(h1[e][k], lo, hi);
+          r[e] = pack2(fmaxf(lo, 0.f), fmaxf(hi, 0.f));
+        }
+#pragma unroll
+        for (int j = 0; j < H; j += 2) {
+          const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(&s_w[W::W2 + (k * H + j) * 2]);
+          h2[0][j] = fma2(w.x, r[0], h2[0][j]); h2[0][j + 1] = fma2(w.y, r[0], h2[0][j + 1]);
+          h2[1][j] = fma2(w.x, r[1], h2[1][j]); h2[1][j + 1] = fma2(w.y, r[1], h2[1][j + 1]);
+        }
+      });
+      // output layer: direction and magnitude
+      const ulonglong2 b3 = *reinterpret_cast<const ulonglong2*>(&s_w[W::B3]);
+      uint64_t o0[2] = {b3.x, b3.x}, o1[2] = {b3.y, b3.y};
+      static_for<0, H>([&](auto kc) {
+        constexpr int k = decltype(kc)::value;
+        const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(&s_w[W::W3 + k * 4]);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          float lo, hi;
+          unpack2(h2[e][k], lo, hi);
+          const uint64_t r = pack2(fmaxf(lo, 0.f), fmaxf(hi, 0.f));
+          o0[e] = fma2(w.x, r, o0[e]);
+          o1[e] = fma2(w.y, r, o1[e]);
+        }
+      });
+      if (colok && x < X) {
+        float d0, d1, d2, d3, m0, m1, m2, m3;
+        unpack2(o0[0], d0, d1); unpack2(o0[1], d2, d3);
+        unpack2(o1[0], m0, m1); unpack2(o1[1], m2, m3);
+        st4(op + (int64_t)x * Y + y, make_float4(finish<FAM>(cp.x, d0, m0, fin), finish<FAM>(cp.y, d1, m1, fin),
+                                                 finish<FAM>(cp.z, d2, m2, fin), finish<FAM>(cp.w, d3, m3, fin)));
+      }
+      if (q + 1 < PK_ROWS) { cg = ng_; cp = np_; cm0 = nm0; cm1 = nm1; cm2 = nm2; cv = nv; }
     }
   }
 }
@@ -1203,35 +1397,56 @@ __global__ void k_velo_xmix(const pylo_velo_rnn r) {
   r.xmix[e] = acc + r.pooled[h];
 }
 
-// gates[t][q] = lstm_b[q] + sum_k lstm_w[q][k] * cat(x', h)[t][k].  One warp per (q, block of 8 rows t).
-#define GATE_TB 8
+// gates[t][q] = lstm_b[q] + sum_k lstm_w[q][k] * cat(x', h)[t][k]: a [T x 2H] x [2H x 4H] product.
+// Shared-memory tiled, 64 x 64 outputs per CTA, 16 deep, 4 x 4 outputs per thread; fp32 throughout
+// (the whole product is ~1 GFLOP, far too small to be worth a tensor-core path).
+#define GT 64
+#define GK 16
 __global__ void __launch_bounds__(NT) k_velo_gates(const pylo_velo_rnn r) {
-  const int lane = threadIdx.x & 31;
-  const int64_t wid = (int64_t)blockIdx.x * NWARP + (threadIdx.x >> 5);
-  const int H = r.H, Q = 4 * H, K = 2 * H;
-  const int tblocks = (r.T + GATE_TB - 1) / GATE_TB;
-  if (wid >= (int64_t)Q * tblocks) return;
-  const int q = (int)(wid % Q), tb = (int)(wid / Q);
-  const int t0 = tb * GATE_TB;
-  float acc[GATE_TB];
+  __shared__ float s_a[GK][GT + 4];
+  __shared__ float s_w[GK][GT + 4];
+  const int H = r.H, Q = 4 * H, K = 2 * H, T = r.T;
+  const int t0 = blockIdx.y * GT, q0 = blockIdx.x * GT;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // 16 x 16 threads
+  float acc[4][4];
 #pragma unroll
-  for (int u = 0; u < GATE_TB; ++u) acc[u] = 0.f;
-  const float* wrow = r.lstm_w + (int64_t)q * K;
-  for (int k = lane; k < K; k += 32) {
-    const float w = wrow[k];
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int u = 0; u < GATE_TB; ++u) {
-      const int t = t0 + u;
-      if (t < r.T) {
-        const float xv = k < H ? r.xmix[(int64_t)t * H + k] : r.h[(int64_t)t * H + (k - H)];
-        acc[u] = fmaf(w, xv, acc[u]);
-      }
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += GK) {
+    // each thread loads 4 elements of each operand tile: rows (threadIdx.x / 16 + 16 * u), column threadIdx.x % 16
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int row = ty + 16 * u, kk = k0 + tx;
+      const int t = t0 + row, q = q0 + row;
+      float av = 0.f, wv = 0.f;
+      if (t < T && kk < K) av = kk < H ? r.xmix[(int64_t)t * H + kk] : r.h[(int64_t)t * H + (kk - H)];
+      if (q < Q && kk < K) wv = r.lstm_w[(int64_t)q * K + kk];
+      s_a[tx][row] = av;
+      s_w[tx][row] = wv;
     }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < GK; ++kk) {
+      const float4 a = ld4(&s_a[kk][ty * 4]);
+      const float4 w = ld4(&s_w[kk][tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+    __syncthreads();
   }
 #pragma unroll
-  for (int u = 0; u < GATE_TB; ++u) {
-    const float s = warp_sum(acc[u]);
-    if (lane == 0 && t0 + u < r.T) r.gates[(int64_t)(t0 + u) * Q + q] = s + r.lstm_b[q];
+  for (int i = 0; i < 4; ++i) {
+    const int t = t0 + ty * 4 + i;
+    if (t >= T) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int q = q0 + tx * 4 + j;
+      if (q < Q) r.gates[(int64_t)t * Q + q] = acc[i][j] + r.lstm_b[q];
+    }
   }
 }
 
@@ -1372,12 +1587,14 @@ int pylo_b200_grad_sumsq_static(const pylo_gvec* items, const pylo_tile* tiles, 
 }
 
 int pylo_b200_rowcol_sums(const pylo_tensor_desc* descs, const pylo_atile* atiles, int n_atiles,
-                          const int32_t* generic_ids, int n_generic, const pylo_step_params* prm, void* stream) {
-  CHECK_ARG(descs && prm && n_atiles >= 0 && n_generic >= 0);
+                          const pylo_atile* rtiles, int n_rtiles, const int32_t* generic_ids, int n_generic,
+                          const pylo_step_params* prm, void* stream) {
+  CHECK_ARG(descs && prm && n_atiles >= 0 && n_rtiles >= 0 && n_generic >= 0);
   cudaStream_t s = (cudaStream_t)stream;
   if (n_atiles > 0) {
-    CHECK_ARG(atiles);
+    CHECK_ARG(atiles && rtiles && n_rtiles > 0);
     k_rowcol_fast<<<grid_for(n_atiles, 4), NT, 0, s>>>(descs, atiles, n_atiles, *prm);
+    k_colpart_reduce<<<grid_for(n_rtiles, 8), NT, 0, s>>>(descs, rtiles, n_rtiles);
   }
   if (n_generic > 0) {
     CHECK_ARG(generic_ids);
@@ -1463,6 +1680,19 @@ int pylo_b200_apply_adafac_cols(const pylo_tensor_desc* descs, const pylo_atile*
   return launch_status();
 }
 
+int pylo_b200_apply_packed(const pylo_tensor_desc* descs, const pylo_atile* ctiles, int n_ctiles,
+                           const pylo_step_params* prm, void* stream) {
+  CHECK_ARG(descs && ctiles && prm && n_ctiles >= 0);
+  if (n_ctiles == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (prm->family) {
+    case PYLO_FAM_CELO2: k_apply_packed<PYLO_FAM_CELO2><<<grid_for(n_ctiles, 2), NT, 0, s>>>(descs, ctiles, n_ctiles, *prm); break;
+    case PYLO_FAM_VELO: k_apply_packed<PYLO_FAM_VELO><<<grid_for(n_ctiles, 2), NT, 0, s>>>(descs, ctiles, n_ctiles, *prm); break;
+    default: return -2;
+  }
+  return launch_status();
+}
+
 int pylo_b200_celo2_post_sums(const pylo_post_item* items, const pylo_tile* tiles, int n_tiles, void* stream) {
   CHECK_ARG(items && tiles && n_tiles >= 0);
   if (n_tiles == 0) return 0;
@@ -1502,8 +1732,7 @@ int pylo_b200_velo_rnn(const pylo_velo_rnn* rnn, void* stream) {
   const int64_t TH = (int64_t)r.T * r.H;
   k_velo_pool<<<(r.H + 127) / 128, 128, 0, s>>>(r);
   k_velo_xmix<<<(unsigned)((TH + 255) / 256), 256, 0, s>>>(r);
-  const int64_t gw = (int64_t)4 * r.H * ((r.T + GATE_TB - 1) / GATE_TB);
-  k_velo_gates<<<(unsigned)((gw + NWARP - 1) / NWARP), NT, 0, s>>>(r);
+  k_velo_gates<<<dim3((4 * r.H + GT - 1) / GT, (r.T + GT - 1) / GT), NT, 0, s>>>(r);
   k_velo_cell<<<(unsigned)((TH + 255) / 256), 256, 0, s>>>(r);
   const int64_t hw = (int64_t)r.T * (r.B + 1);
   k_velo_heads<<<(unsigned)((hw + NWARP - 1) / NWARP), NT, 0, s>>>(r);

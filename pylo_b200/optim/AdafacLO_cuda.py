@@ -50,6 +50,9 @@ class _AdafacFamily(Optimizer):
         self._w_flat = torch.cat([t.reshape(-1) for t in flat]).to(self.device).contiguous()
         self._plans = {}
         self._gnorm = None
+        # fp32 values of 1 - beta, read back once (the reference evaluates them on the device every step)
+        self._w_m, self._w_f = one_minus(self.beta_m), one_minus(self.beta_adafactor)
+        self._w_v = one_minus(self.beta_rms)[0]
 
     def _init_state(self, state, p):
         """AdafacLO_cuda.py:227-256 / ELO_cuda.py:160-176."""
@@ -118,10 +121,9 @@ class _AdafacFamily(Optimizer):
         prm = L.StepParams()
         prm.family = L.FAM_ADAFAC
         prm.nan_to_num, prm.wd_mode = int(nan_to_num), int(wd_mode)
-        wm, wf = one_minus(self.beta_m), one_minus(self.beta_adafactor)
         for k in range(3):
-            prm.w_m[k], prm.w_f[k] = wm[k], wf[k]
-        prm.w_v = one_minus(self.beta_rms)[0]
+            prm.w_m[k], prm.w_f[k] = self._w_m[k], self._w_f[k]
+        prm.w_v = self._w_v
         prm.eps_v, prm.eps_feat, prm.eps_norm = 1e-30, 1e-6, 1e-5
         prm.clip_val = float("inf")
         prm.gnorm_sq = gnorm_ptr

@@ -22,6 +22,7 @@ from __future__ import annotations
 import ctypes as C
 from typing import Optional
 
+import numpy as np
 import torch
 from torch.optim import Optimizer
 
@@ -71,6 +72,10 @@ class _Celo2Family(Optimizer):
         self._w_flat = torch.cat([t.reshape(-1) for t in (self.w_in, self.b_in, self.w_h, self.b_h, self.w_out, self.b_out)]).contiguous()
         self._plans = {}
         self._gnorm = None
+        # fp32 values of 1 - beta, read back once (the reference evaluates them on the device every step)
+        self._w_m, self._w_f = one_minus(self.beta_m), one_minus(self.beta_fac)
+        self._w_v = float(1 - self.beta_rms[-1])
+        self._b1_shared, self._b2_shared = float(self.beta_m[0]), float(self.beta_rms[-1])
 
     # ------------------------------------------------------------------ state
     def _init_lo_state(self, state, p):
@@ -138,6 +143,8 @@ class _Celo2Family(Optimizer):
                     post_owner.append((ti, k * mat))
             post = ItemPlan(L.POST_DTYPE, post_sizes, self.device)
             post.owner = post_owner
+            post.owner_t = np.array([t for t, _ in post_owner], dtype=np.int64)
+            post.owner_off = np.array([4 * o for _, o in post_owner], dtype=np.uint64)
             post.part = torch.zeros(max(post.n_tiles, 1), dtype=torch.float32, device=self.device)
             for i, (t0, k) in enumerate(post.ranges):
                 post.items["part"][i] = post.part.data_ptr() + 4 * t0
@@ -150,10 +157,9 @@ class _Celo2Family(Optimizer):
         prm = L.StepParams()
         prm.family = L.FAM_CELO2
         prm.nan_to_num, prm.wd_mode = 0, 0
-        wm, wf = one_minus(self.beta_m), one_minus(self.beta_fac)
         for k in range(3):
-            prm.w_m[k], prm.w_f[k] = wm[k], wf[k]
-        prm.w_v = float(1 - self.beta_rms[-1])
+            prm.w_m[k], prm.w_f[k] = self._w_m[k], self._w_f[k]
+        prm.w_v = self._w_v
         prm.eps_v, prm.eps_feat, prm.eps_norm = 0.0, 1e-8, 1e-9
         prm.clip_val = float(group["grad_clip_val"])
         prm.gnorm_sq = gnorm_ptr
@@ -204,9 +210,10 @@ class _Celo2Family(Optimizer):
                         step = newton_schulz(step, self.ns_coeffs, self.ns_iters, self.ns_eps).contiguous()
                     keep.append(step)
                 it = post.items
-                for i, (ti, off) in enumerate(post.owner):
-                    it["step"][i] = keep[ti].data_ptr() + 4 * off
-                    it["p"][i] = plan["lo_params"][ti].data_ptr() + 4 * off
+                base_s = np.fromiter((k.data_ptr() for k in keep), dtype=np.uint64, count=len(keep))
+                base_p = np.fromiter((p.data_ptr() for p in plan["lo_params"]), dtype=np.uint64, count=len(keep))
+                it["step"][:] = base_s[post.owner_t] + post.owner_off
+                it["p"][:] = base_p[post.owner_t] + post.owner_off
                 it["lr"][:] = lr
                 it["wd"][:] = group["weight_decay"]
                 it["rmsmult"][:] = group["rmsmult"]
@@ -228,7 +235,7 @@ class _Celo2Family(Optimizer):
                     it["g"][i], it["p"][i] = g.data_ptr(), p.data_ptr()
                     if self._shared_adam:
                         t = group["step"]
-                        b1, b2 = float(self.beta_m[0]), float(self.beta_rms[-1])
+                        b1, b2 = self._b1_shared, self._b2_shared
                         it["m"][i], it["v"][i] = st["mom"].data_ptr(), st["rms"].data_ptr()
                     else:
                         st["adam_step"] += 1

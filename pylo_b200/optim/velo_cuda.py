@@ -114,6 +114,9 @@ class VeLO_CUDA(Optimizer):
         if self._bank.shape != (self._B, 159) or sd["mix_layer2.weight"].shape[1] != 30:
             raise ValueError("VeLO_CUDA kernels are built for 30 LSTM inputs and the 30-4-4-3 per-element network")
         self._plan = None
+        g0 = self.param_groups[0]
+        self._w_m, self._w_f = one_minus(g0["initial_momentum_decays"]), one_minus(g0["initial_adafactor_decays"])
+        self._w_v = one_minus(g0["initial_rms_decays"])[0]
         self.init_state()
 
     @torch.no_grad()
@@ -254,13 +257,11 @@ class VeLO_CUDA(Optimizer):
                                                    buf["loss"].data_ptr(), buf["loss9"].data_ptr(), stream), "velo_loss_features")
         buf["fraction9"].copy_(fractional_tanh_embed(fraction), non_blocking=True)
 
-        group0 = self.param_groups[0]
         prm = L.StepParams()
         prm.family, prm.nan_to_num, prm.wd_mode = L.FAM_VELO, 0, 3
-        wm, wf = one_minus(group0["initial_momentum_decays"]), one_minus(group0["initial_adafactor_decays"])
         for k in range(3):
-            prm.w_m[k], prm.w_f[k] = wm[k], wf[k]
-        prm.w_v = one_minus(group0["initial_rms_decays"])[0]
+            prm.w_m[k], prm.w_f[k] = self._w_m[k], self._w_f[k]
+        prm.w_v = self._w_v
         prm.eps_v, prm.eps_feat, prm.eps_norm = 0.0, 1e-6, 1e-5
         prm.clip_val = 1000.0
         prm.gnorm_sq = None

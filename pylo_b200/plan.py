@@ -88,6 +88,7 @@ class DeviceTable:
         self._stage = [torch.empty(self.nbytes, dtype=torch.uint8).pin_memory() for _ in range(2)]
         self._events = [None, None]
         self._turn = 0
+        self._last = None
         self.upload()
 
     @property
@@ -95,6 +96,11 @@ class DeviceTable:
         return self.dev.data_ptr()
 
     def upload(self):
+        """Copy the host array to the device unless it still holds exactly these bytes."""
+        raw = self.host.view(np.uint8).reshape(-1) if self.host.nbytes else None
+        if raw is not None and self._last is not None and np.array_equal(raw, self._last):
+            return
+        self._last = None if raw is None else raw.copy()
         i = self._turn
         self._turn ^= 1
         if self._events[i] is not None:
@@ -125,7 +131,7 @@ class LoPlan:
         H = self.H[family]
         tdesc = np.zeros(T, dtype=L.DESC_DTYPE)
         ws_items = []  # (table, row, field, count)
-        atiles, generic = [], []
+        atiles, rtiles, generic = [], [], []
         for i, t in enumerate(tensors):
             shape = tuple(t.p.shape)
             n = t.p.numel()
@@ -166,15 +172,16 @@ class LoPlan:
                 d["mode"] = L.MODE_FAST2D if fast else L.MODE_GENERIC
                 ws_items += [("t", i, "f_a", 3 * La), ("t", i, "f_b", 3 * Lb), ("t", i, "sum_a", La), ("t", i, "sum_b", Lb)]
                 if fast:
-                    rb = max(8, ((X + 63) // 64 + 7) // 8 * 8)
+                    rb = min(128, max(32, ((X + 127) // 128 + 7) // 8 * 8))  # rows per strip
                     n_strips = (X + rb - 1) // rb
                     n_cb = (Y + L.A_COLS - 1) // L.A_COLS
                     d["rb"], d["n_strips"], d["n_cb"] = rb, n_strips, n_cb
                     ws_items += [("t", i, "fx", 4 * La), ("t", i, "part_a", X * n_cb), ("t", i, "part_b", n_strips * Y),
-                                 ("t", i, "h_a", La * H), ("t", i, "h_b", Lb * H)]
+                                 ("t", i, "h_a", La * H * 2), ("t", i, "h_b", Lb * H)]
                     for s in range(n_strips):
                         for cb in range(n_cb):
                             atiles.append((i, s, cb, 0))
+                    rtiles += [(i, 0, cb, 0) for cb in range(n_cb)]
                 else:
                     generic.append(i)
             ws_items.append(("t", i, "closed", L.STAT_STRIDE))
@@ -232,30 +239,37 @@ class LoPlan:
         self.n_tiles = len(tiles)
         self.atiles = DeviceTable(np.array(atiles, dtype=np.int32).reshape(-1, 4).view(L.ATILE_DTYPE).reshape(-1), self.device)
         self.n_atiles = len(atiles)
+        self.rtiles = DeviceTable(np.array(rtiles, dtype=np.int32).reshape(-1, 4).view(L.ATILE_DTYPE).reshape(-1), self.device)
+        self.n_rtiles = len(rtiles)
         self.generic = DeviceTable(np.array(generic, dtype=np.int32), self.device)
         self.n_generic = len(generic)
         self.n_tensors = T
         self.n_units = U
         self.total_elems = int(sum(sizes))
         self._keepalive = []
-        # AdafacLO / ELO: FAST2D tensors take the thread-owns-column apply kernel, the rest the generic one
-        self.ctiles = None
-        if family == L.FAM_ADAFAC:
-            ctiles = []
-            for i in range(T):
-                if tdesc["mode"][i] != L.MODE_FAST2D:
-                    continue
-                X, Y = int(tdesc["X"][i]), int(tdesc["Y"][i])
+        # FAST2D tensors take a column-owning apply kernel (AdafacLO/ELO: one column per thread, 16 or 32 rows;
+        # CELO2/VeLO: four columns per thread, 8 rows per thread); everything else the generic one
+        ctiles = []
+        unit_of = {i: u for u, (i, _) in enumerate(unit_owner)}  # a FAST2D tensor is never sliced: one unit
+        for i in range(T):
+            if tdesc["mode"][i] != L.MODE_FAST2D:
+                continue
+            X, Y = int(tdesc["X"][i]), int(tdesc["Y"][i])
+            if family == L.FAM_ADAFAC:
                 cw = min((256, 128, 64, 32), key=lambda c: ((Y + c - 1) // c * c - Y, -c))
-                rt = 16 if cw == 256 else 32
-                for rtile in range((X + rt - 1) // rt):
-                    for ctile in range((Y + cw - 1) // cw):
-                        ctiles.append((i, rtile, ctile, cw))
-            self.ctiles = DeviceTable(np.array(ctiles, dtype=np.int32).reshape(-1, 4).view(L.ATILE_DTYPE).reshape(-1), self.device)
-            self.n_ctiles = len(ctiles)
-            slow = np.array([t for t in tiles if udesc["mode"][t["tensor"]] != L.MODE_FAST2D], dtype=L.TILE_DTYPE)
-            self.tiles_slow = DeviceTable(slow, self.device)
-            self.n_tiles_slow = len(slow)
+                rt, width, tag = (16 if cw == 256 else 32), cw, cw
+            else:
+                tpr = min((256, 128, 64, 32, 16, 8), key=lambda c: ((Y + 4 * c - 1) // (4 * c) * 4 * c - Y, -c))
+                rt, width, tag = 8 * (256 // tpr), 4 * tpr, tpr
+            for rtile in range((X + rt - 1) // rt):
+                for ctile in range((Y + width - 1) // width):
+                    ctiles.append((unit_of[i], rtile, ctile, tag))
+        self.ctiles = DeviceTable(np.array(ctiles, dtype=np.int32).reshape(-1, 4).view(L.ATILE_DTYPE).reshape(-1), self.device)
+        self.n_ctiles = len(ctiles)
+        fast_unit = udesc["mode"] == L.MODE_FAST2D
+        slow = tiles[~fast_unit[tiles["tensor"]]] if len(tiles) else tiles
+        self.tiles_slow = DeviceTable(np.ascontiguousarray(slow), self.device)
+        self.n_tiles_slow = len(slow)
 
     # ------------------------------------------------------------------ per-step refresh
     def set_field(self, name, values):
@@ -311,9 +325,8 @@ class LoPlan:
         pp = C.byref(prm)
         if self.n_atiles or self.n_generic:
             self._call("rowcol_sums", L.lib.pylo_b200_rowcol_sums, self.tdesc.ptr, self.atiles.ptr, self.n_atiles,
-                       self.generic.ptr, self.n_generic, pp, stream)
-            if self.n_atiles and self.n_generic:
-                self.launch_count += 1
+                       self.rtiles.ptr, self.n_rtiles, self.generic.ptr, self.n_generic, pp, stream)
+            self.launch_count += (1 if self.n_atiles else 0) + (1 if self.n_atiles and self.n_generic else 0)
         self._call("factor_update", L.lib.pylo_b200_factor_update, self.tdesc.ptr, self.n_tensors, pp, stream)
         self._call("state_moments", L.lib.pylo_b200_state_moments, self.desc.ptr, self.tiles.ptr, self.n_tiles,
                    int(reverse_b), pp, stream)
@@ -323,13 +336,11 @@ class LoPlan:
         """Phases P, C."""
         pp = C.byref(prm)
         self._call("prep_apply", L.lib.pylo_b200_prep_apply, self.desc.ptr, self.n_units, pp, stream)
-        if self.ctiles is not None:
-            if self.n_ctiles:
-                self._call("apply_cols", L.lib.pylo_b200_apply_adafac_cols, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp, stream)
-            if self.n_tiles_slow:
-                self._call("apply", L.lib.pylo_b200_apply, self.desc.ptr, self.tiles_slow.ptr, self.n_tiles_slow, int(reverse_c), pp, stream)
-        else:
-            self._call("apply", L.lib.pylo_b200_apply, self.desc.ptr, self.tiles.ptr, self.n_tiles, int(reverse_c), pp, stream)
+        if self.n_ctiles:
+            fn = L.lib.pylo_b200_apply_adafac_cols if self.family == L.FAM_ADAFAC else L.lib.pylo_b200_apply_packed
+            self._call("apply_cols", fn, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp, stream)
+        if self.n_tiles_slow:
+            self._call("apply", L.lib.pylo_b200_apply, self.desc.ptr, self.tiles_slow.ptr, self.n_tiles_slow, int(reverse_c), pp, stream)
 
 
 class GradNorm:
