@@ -1,0 +1,200 @@
+"""GPU checks beyond the golden trajectories: resume format, ragged shapes, full-size properties.
+
+At the full BASELINE size (4096 x 4096) the oracle would take minutes per family, so the checks there
+are size-independent properties: two different code paths of the library (the float4 path and the
+scalar generic path, selected by the alignment of the tensors) must agree, and repeated runs must be
+bit-identical.
+"""
+
+import copy
+
+import pytest
+import torch
+
+import cases
+import cuda_util as CU
+import golden_util as G
+
+pytestmark = pytest.mark.gpu
+
+
+def _nets(family):
+    from pylo_b200 import models
+
+    torch.manual_seed(0)
+    if family in ("adafaclo", "elo"):
+        return models.MetaMLP(39, 32, 1)
+    if family in ("celo2", "elo_celo2"):
+        return models.CELO2MLP()
+    rnn, mlp = models.VeLORNN(lstm_hidden_size=32), models.VeLOMLP()
+    with torch.no_grad():
+        for name, p in mlp.named_parameters():
+            if name.endswith("_") or "_." in name:
+                p.mul_(0.05)
+    return rnn, mlp
+
+
+def _make(family, params, **kw):
+    from pylo_b200 import optim
+
+    if family == "adafaclo":
+        return optim.AdafacLO_CUDA(params, lr=1e-2, network=_nets(family), **kw)
+    if family == "elo":
+        return optim.ELO_CUDA(params, lr=1e-2, weight_decay=0.1, clip_grad=True, network=_nets(family), **kw)
+    if family == "celo2":
+        return optim.CELO2_CUDA(params, lr=1e-2, weight_decay=0.1, clip_grad=True, network=_nets(family), **kw)
+    if family == "elo_celo2":
+        return optim.ELO_CELO2_CUDA(params, lr=1e-2, network=_nets(family), **kw)
+    rnn, mlp = _nets(family)
+    return optim.VeLO_CUDA(params, lr=kw.pop("lr", 1.0), num_steps=100, rnn=rnn, mlp=mlp, **kw)
+
+
+def _step(opt, family, t):
+    if family == "velo":
+        opt.step(torch.tensor(cases.velo_loss(t), device="cuda"))
+    else:
+        opt.step()
+
+
+FAMILIES = ["adafaclo", "elo", "celo2", "elo_celo2", "velo"]
+RAGGED = [(33, 7), (1, 5), (5, 1), (17, 36), (3, 3, 3), (1,), (7,), (257, 129), (2, 4100)]
+
+
+@pytest.mark.parametrize("family", FAMILIES)
+def test_ragged_shapes_match_oracle(family):
+    """Sizes that are not multiples of 4 / 32 / 256, single rows and columns, one-element vectors."""
+    case = dict(name="ragged", family=family, shapes=RAGGED, net_seed=0, init_seed=5, init_scale=0.1, grad_seed=6,
+                grad_scale=0.3, steps=3, record=[1, 3], hparams={})
+    dev = "cuda"
+    params = [torch.nn.Parameter(v.to(dev)) for v in cases.init_values(case)]
+    opt = _make(family, params)
+    from oracle import pylo_oracle as O
+
+    net = _nets(family)
+    if family in ("adafaclo", "elo"):
+        kw = dict(lr=1e-2, elo=(family == "elo"))
+        if family == "elo":
+            kw.update(weight_decay=0.1, clip_grad=True)
+        ora = O.AdafacLOOracle(net.flat_weights(), **kw)
+    elif family in ("celo2", "elo_celo2"):
+        kw = dict(lr=1e-2, shared_adam=(family == "elo_celo2"))
+        kw.update(dict(weight_decay=0.1, clip_grad=True) if family == "celo2" else dict(weight_decay=0.1, clip_grad=True, adam_lr_mult=20.0))
+        ora = O.CELO2Oracle(net.flat_weights(), **kw)
+    else:
+        rnn, mlp = net
+        ora = O.VeLOOracle(O.rnn_weights_from_module(rnn), O.bank_from_module(mlp), RAGGED, lr=1.0, num_steps=100)
+    ref = [v.clone() for v in cases.init_values(case)]
+    init = [v.clone() for v in ref]
+    for t in (1, 2, 3):
+        grads = cases.grads_at(case, t)
+        for p, g in zip(params, grads):
+            p.grad = g.to(dev)
+        _step(opt, family, t)
+        if family == "velo":
+            ora.step(ref, grads, cases.velo_loss(t))
+        else:
+            ora.step(ref, grads)
+    got = {3: [p.detach().cpu() for p in params]}
+    res = CU.compare(got, {3: ref}, init)
+    assert res[3][0] < 1e-5 and res[3][1] < 2e-3, res
+
+
+@pytest.mark.parametrize("family", FAMILIES)
+def test_resume_from_state_dict_continues_identically(family):
+    """Save after 3 steps, load into a fresh optimizer, continue: same parameters as the uninterrupted run
+    (the contract of the reference's tests/test_optimizer_resume.py:134-164)."""
+    shapes = [(40, 24), (24, 40), (24,)]
+    case = dict(shapes=shapes, init_seed=9, grad_seed=10, grad_scale=0.5)
+
+    def fresh():
+        ps = [torch.nn.Parameter(v.cuda()) for v in cases.init_values(case)]
+        return ps, _make(family, ps)
+
+    pa, oa = fresh()
+    for t in range(1, 7):
+        for p, g in zip(pa, cases.grads_at(case, t)):
+            p.grad = g.cuda()
+        _step(oa, family, t)
+        if t == 3:
+            saved = copy.deepcopy(oa.state_dict())
+            saved_p = [p.detach().clone() for p in pa]
+    pb, ob = fresh()
+    with torch.no_grad():
+        for p, v in zip(pb, saved_p):
+            p.copy_(v)
+    ob.load_state_dict(saved)
+    for t in range(4, 7):
+        for p, g in zip(pb, cases.grads_at(case, t)):
+            p.grad = g.cuda()
+        _step(ob, family, t)
+    for a, b in zip(pa, pb):
+        assert torch.allclose(a, b, rtol=1e-6, atol=1e-7)
+
+
+def test_state_keys_and_shapes_are_the_reference_format():
+    shape = (12, 20)
+    p = [torch.nn.Parameter(torch.randn(shape, device="cuda")), torch.nn.Parameter(torch.randn(20, device="cuda"))]
+    for q in p:
+        q.grad = torch.randn_like(q)
+    opt = _make("adafaclo", p)
+    opt.step()
+    st = opt.state[p[0]]
+    assert st["step"].dtype == torch.float64 and st["step"].device.type == "cpu" and float(st["step"]) == 1.0
+    assert tuple(st["exp_avg"].shape) == (3,) + shape and tuple(st["exp_avg_sq"].shape) == shape
+    assert tuple(st["exp_avg_sq_r"].shape) == (3, 12, 1) and tuple(st["exp_avg_sq_c"].shape) == (3, 1, 20)
+    assert tuple(opt.state[p[1]]["exp_avg_sq_r"].shape) == (3, 20)
+    opt = _make("celo2", p)
+    opt.step()
+    st = opt.state[p[0]]
+    assert tuple(st["mom"].shape) == (3,) + shape and tuple(st["fac_r"].shape) == (3, 12, 1)
+    assert set(opt.state[p[1]]) == {"exp_avg", "exp_avg_sq", "adam_step"}
+    opt = _make("velo", p)
+    opt.step(torch.tensor(1.0, device="cuda"))
+    st = opt.state[p[0]]
+    assert tuple(st["rms"].shape) == (1,) + shape and tuple(st["fac_vec_row"].shape) == (3, 12, 1)
+    assert st["fac_vec_v"].numel() == 0 and tuple(opt.state[p[1]]["fac_vec_v"].shape) == (3, 20)
+    sd = opt.state_dict()
+    assert {"loss_buffer", "lstm_hidden_state", "num_steps"} <= set(sd)
+
+
+@pytest.mark.parametrize("family", ["adafaclo", "celo2", "velo"])
+def test_full_size_float4_and_generic_paths_agree(family):
+    """4096 x 4096 (the BASELINE single-tensor size): the same values once 16-byte aligned (float4 path)
+    and once shifted by one float (scalar generic path) must give the same update."""
+    n = 4096
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    w0 = torch.randn(n, n, device="cuda", generator=gen) * 0.02
+    row = torch.exp(-7 + torch.randn(n, 1, device="cuda", generator=gen))
+    outs = []
+    for shift in (0, 1):
+        buf = torch.empty(n * n + 4, device="cuda")
+        view = buf[shift:shift + n * n].view(n, n)
+        view.copy_(w0)
+        p = torch.nn.Parameter(view)
+        kw = {"orthogonalize": False} if family == "celo2" else ({"lr": 1e3} if family == "velo" else {})
+        opt = _make(family, [p], **kw)
+        for t in (1, 2):
+            g = torch.Generator(device="cuda").manual_seed(100 + t)
+            p.grad = torch.randn(n, n, device="cuda", generator=g) * row
+            _step(opt, family, t)
+        outs.append(p.detach().clone())
+        del opt
+    a, b = outs
+    moved = (a - w0).abs().max()
+    assert moved > 0
+    err = torch.clamp((a - b).abs() - 4 * 1.2e-7 * a.abs(), min=0).max()
+    assert float(err / moved) < 1e-3
+    assert torch.allclose(a, b, rtol=1e-5, atol=1e-7)
+
+
+def test_full_size_is_bit_reproducible():
+    n = 4096
+    outs = []
+    for _ in range(2):
+        gen = torch.Generator(device="cuda").manual_seed(3)
+        p = torch.nn.Parameter(torch.randn(n, n, device="cuda", generator=gen) * 0.02)
+        opt = _make("adafaclo", [p])
+        p.grad = torch.randn(n, n, device="cuda", generator=gen) * 1e-3
+        opt.step()
+        outs.append(p.detach().clone())
+    assert torch.equal(outs[0], outs[1])
