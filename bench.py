@@ -35,6 +35,9 @@ STEP_BYTES = {"adafaclo": 44, "elo": 44, "velo": 44, "celo2": 56, "elo_celo2": 5
 # compulsory bytes per parameter of the apply sweep alone (reads g, p, m(3), v; writes p or the raw step)
 APPLY_BYTES = 28
 B_BYTES = 40  # state_moments sweep: reads g, p, m(3), v; writes m(3), v
+# DRAM bytes per element (dram__bytes_read.sum + dram__bytes_write.sum) of each dominant kernel, from ncu
+# captures of a 4096 x 4096 case (profiles/*.md); traffic grows in proportion to the elements processed
+NCU_TRAFFIC_PER_ELEM = {("adafaclo", "apply_cols"): 27.45, ("elo", "apply_cols"): 27.45}
 
 
 def parse():
@@ -370,7 +373,10 @@ def run_b200(args):
         achieved = per_launch_elems * kbytes / (phase_ms.get(dominant, 1e9) * 1e-3) / 1e9 if dominant else 0.0
         roofline = {
             "bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
-            "frac": achieved / peak, "peak_source": f"{peak_src} (MEASURED_PEAKS.json hbm_gbs)", "traffic": None,
+            "frac": achieved / peak, "peak_source": f"{peak_src} (MEASURED_PEAKS.json hbm_gbs)",
+            "traffic": (NCU_TRAFFIC_PER_ELEM[(args.optimizer, dominant)] * per_launch_elems
+                        if (args.optimizer, dominant) in NCU_TRAFFIC_PER_ELEM else None),
+            "traffic_note": "ncu dram bytes per element of a 4096x4096 capture x elements per launch",
             "algorithmic_bytes_per_param": kbytes, "avg_launch_ms": phase_ms.get(dominant),
             "phase_ms_per_launch": phase_ms,
             "step": {"algorithmic_bytes_per_param": STEP_BYTES[args.optimizer],
