@@ -85,23 +85,27 @@ def seeded_networks(kind):
     return rnn, mlp
 
 
-def build_optimizer(args, params, is_embedding=None):
+def build_optimizer(args, shard, params, is_embedding=None):
     from pylo_b200 import optim
 
     k = args.optimizer
     if k == "adafaclo":
         return optim.AdafacLO_CUDA(params, lr=1e-3, step_mult=0.01, exp_mult=0.001, network=seeded_networks(k))
     if k == "elo":
-        return optim.ELO_CUDA(params, lr=1e-3, weight_decay=0.1, clip_grad=True, network=seeded_networks(k))
-    if k in ("celo2", "elo_celo2"):
+        opt = optim.ELO_CUDA(params, lr=1e-3, weight_decay=0.1, clip_grad=True, network=seeded_networks(k))
+    elif k in ("celo2", "elo_celo2"):
         groups = [{"params": [p for p, e in zip(params, is_embedding) if not e]},
                   {"params": [p for p, e in zip(params, is_embedding) if e], "is_embedding": True}]
         groups = [g for g in groups if g["params"]]
         cls = optim.CELO2_CUDA if k == "celo2" else optim.ELO_CELO2_CUDA
         kw = dict(lr=1e-3, weight_decay=0.1, orthogonalize=not args.no_orthogonalize, network=seeded_networks(k))
-        return cls(groups, **kw)
-    rnn, mlp = seeded_networks(k)
-    return optim.VeLO_CUDA(params, lr=1e-3, num_steps=10000, rnn=rnn, mlp=mlp)
+        opt = cls(groups, **kw)
+    else:
+        rnn, mlp = seeded_networks(k)
+        return optim.VeLO_CUDA(params, lr=1e-3, num_steps=10000, rnn=rnn, mlp=mlp, process_group=shard.pg,
+                               all_shapes=[tuple(p.shape) for p in shard.params], owned=shard.owned)
+    opt._sharded, opt.process_group = shard.world > 1, shard.pg
+    return opt
 
 
 class ClockSampler:
@@ -259,7 +263,7 @@ def run_b200(args):
     for p in params:
         p.grad = pool[tuple(p.shape)]
     emb = [shapes[i][0] > 32768 for i in owned]  # token embedding / lm head go to the AdamW branch in the CELO2 family
-    opt = build_optimizer(args, params, emb)
+    opt = build_optimizer(args, shard, params, emb)
     owned_n = sum(p.numel() for p in params)
     velo = args.optimizer == "velo"
     loss = torch.tensor(1.0, device=dev)

@@ -264,6 +264,9 @@ int pylo_b200_adamw(const pylo_adam_item* items, const pylo_tile* tiles, int n_t
 
 /* VeLO front end.  velo_tensor_features: desc.sums -> the [T][30] LSTM input rows, row T-1-t for
  * tensor t (velo_cuda.py:213-252,419-422); loss features and fraction features are passed in.
+ * When the tensors are sharded over ranks, descs holds this rank's n_local tensors, layer_of[i] is the
+ * position of local tensor i among all n_total tensors (NULL: identity), rank_onehot is [n_local][5]; the
+ * caller zeroes x_in first and sums it over the ranks afterwards.
  * velo_rnn: mix layers, LSTM cell, control and step-size heads, bank mixing (VeLO_RNN.py:110-135,
  * VeLO_MLP.py:92-126).  Outputs: weights [T][160] (row per tensor, tensor order), lr_mult [T]. */
 typedef struct pylo_velo_rnn {
@@ -282,8 +285,9 @@ typedef struct pylo_velo_rnn {
   float *lr_mult;                                 /* out [T] */
   int32_t T, H, B, pad_;
 } pylo_velo_rnn;
-int pylo_b200_velo_tensor_features(const pylo_tensor_desc* descs, int n_tensors, const float* rank_onehot,
-                                   const float* fraction9, const float* loss9, float* x_in, void* stream);
+int pylo_b200_velo_tensor_features(const pylo_tensor_desc* descs, int n_local, const int32_t* layer_of,
+                                   int n_total, const float* rank_onehot, const float* fraction9,
+                                   const float* loss9, float* x_in, void* stream);
 int pylo_b200_velo_rnn(const pylo_velo_rnn* rnn, void* stream);
 /* BufferLossAccumulators.update + features (velo_cuda.py:183-211) on device; state arrays are the
  * loss_buffer tensors means[10], iteration (int32), running_min[10], decays[10]; writes loss9[9]. */

@@ -96,7 +96,7 @@ def _load():
         "pylo_b200_celo2_post_sums": [vp, vp, i32, vp],
         "pylo_b200_celo2_post_apply": [vp, vp, i32, vp],
         "pylo_b200_adamw": [vp, vp, i32, i32, f32, f32, f32, f32, f32, C.POINTER(StepParams), vp],
-        "pylo_b200_velo_tensor_features": [vp, i32, vp, vp, vp, vp, vp],
+        "pylo_b200_velo_tensor_features": [vp, i32, vp, i32, vp, vp, vp, vp, vp],
         "pylo_b200_velo_rnn": [C.POINTER(VeloRnn), vp],
         "pylo_b200_velo_loss_features": [vp, vp, vp, vp, vp, vp, vp],
     }

@@ -794,6 +794,12 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
 #define CC_E 2            // rows a thread processes at once (each weight read feeds CC_E elements)
 #define CC_CTAS_PER_SM 2  // 128 registers per thread
 
+__device__ __forceinline__ float ldg_early(const float* p) {
+  float v;
+  asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+
 struct CcSmem {
   float w[Fold<PYLO_FAM_ADAFAC>::SIZE + 12];  // folded network
   float ha[CC_TILE_ROWS][32];                 // first-layer terms of the tile's rows (bias included)
@@ -861,7 +867,9 @@ __global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const 
         const int x = x0 + rg + ng * (q + e);
         const bool ok = colok && x < X;
         const int64_t idx = ok ? (int64_t)x * Y + y : 0;
-        g[e] = __ldg(gp + idx); p[e] = pp[idx]; m0[e] = mp[idx]; m1[e] = mp[n + idx]; m2[e] = mp[2 * n + idx]; v[e] = vp[idx];
+        // issued as volatile loads so that they stay here, a whole row pair ahead of their use
+        g[e] = ldg_early(gp + idx); p[e] = ldg_early(pp + idx); m0[e] = ldg_early(mp + idx);
+        m1[e] = ldg_early(mp + n + idx); m2[e] = ldg_early(mp + 2 * n + idx); v[e] = ldg_early(vp + idx);
       }
     };
     load_rows(0, cg, cp, cm0, cm1, cm2, cv);
@@ -1309,17 +1317,19 @@ __device__ __forceinline__ float clip_log_abs10(float v) {
 }
 
 // one thread per tensor: the 30 LSTM inputs from the statistics gathered in phase B (velo_cuda.py:213-252)
-__global__ void k_velo_tensor_features(const pylo_tensor_desc* __restrict__ descs, int T,
+__global__ void k_velo_tensor_features(const pylo_tensor_desc* __restrict__ descs, int n_local,
+                                       const int32_t* __restrict__ layer_of, int T,
                                        const float* __restrict__ rank_onehot, const float* __restrict__ fraction9,
                                        const float* __restrict__ loss9, float* __restrict__ x_in) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= T) return;
+  if (t >= n_local) return;
+  const int layer = layer_of ? layer_of[t] : t;  // position of this tensor among all T tensors of the model
   const pylo_tensor_desc& d = descs[t];
   const double n = (double)d.n;
   auto stat = [&](int j) { return (double)d.sums[30 + j] + (double)d.sums[SUMS_LO + j]; };
   const float mean_p2 = (float)((double)d.sums[2] / n);
   const double norm = (double)rsqrtf(fmaxf(mean_p2, 1e-9f));
-  float* o = x_in + (int64_t)(T - 1 - t) * 30;  // rows are flipped (velo_cuda.py:422)
+  float* o = x_in + (int64_t)(T - 1 - layer) * 30;  // rows are flipped (velo_cuda.py:422)
 #pragma unroll
   for (int j = 0; j < 9; ++j) { o[j] = fraction9[j]; o[9 + j] = loss9[j]; }
   const double mean_v = stat(6) / n, e_v2 = stat(7) / n;
@@ -1717,11 +1727,12 @@ int pylo_b200_adamw(const pylo_adam_item* items, const pylo_tile* tiles, int n_t
   return launch_status();
 }
 
-int pylo_b200_velo_tensor_features(const pylo_tensor_desc* descs, int n_tensors, const float* rank_onehot,
-                                   const float* fraction9, const float* loss9, float* x_in, void* stream) {
-  CHECK_ARG(descs && rank_onehot && fraction9 && loss9 && x_in && n_tensors > 0);
-  k_velo_tensor_features<<<(n_tensors + 127) / 128, 128, 0, (cudaStream_t)stream>>>(descs, n_tensors, rank_onehot,
-                                                                                   fraction9, loss9, x_in);
+int pylo_b200_velo_tensor_features(const pylo_tensor_desc* descs, int n_local, const int32_t* layer_of,
+                                   int n_total, const float* rank_onehot, const float* fraction9,
+                                   const float* loss9, float* x_in, void* stream) {
+  CHECK_ARG(descs && rank_onehot && fraction9 && loss9 && x_in && n_local > 0 && n_total >= n_local);
+  k_velo_tensor_features<<<(n_local + 127) / 128, 128, 0, (cudaStream_t)stream>>>(descs, n_local, layer_of, n_total,
+                                                                                 rank_onehot, fraction9, loss9, x_in);
   return launch_status();
 }
 

@@ -72,6 +72,8 @@ class _Celo2Family(Optimizer):
         self._w_flat = torch.cat([t.reshape(-1) for t in (self.w_in, self.b_in, self.w_h, self.b_h, self.w_out, self.b_out)]).contiguous()
         self._plans = {}
         self._gnorm = None
+        self.process_group = None   # set (or set _sharded) when the tensors of the model are split over ranks
+        self._sharded = False
         # fp32 values of 1 - beta, read back once (the reference evaluates them on the device every step)
         self._w_m, self._w_f = one_minus(self.beta_m), one_minus(self.beta_fac)
         self._w_v = float(1 - self.beta_rms[-1])
@@ -175,7 +177,10 @@ class _Celo2Family(Optimizer):
             sig = tuple(p.numel() for p in all_p)
             if self._gnorm is None or self._gnorm[0] != sig:
                 self._gnorm = (sig, GradNorm(sig, self.device))
-            gnorm_ptr = self._gnorm[1].run([p.grad for p in all_p], stream).data_ptr()
+            total = self._gnorm[1].run([p.grad for p in all_p], stream)
+            if self.process_group is not None or (torch.distributed.is_initialized() and self._sharded):
+                torch.distributed.all_reduce(total, group=self.process_group)  # each rank holds its own tensors' share
+            gnorm_ptr = total.data_ptr()
 
         for gi, group in enumerate(self.param_groups):
             plist = [p for p in group["params"] if p.grad is not None]

@@ -67,7 +67,7 @@ class VeLO_CUDA(Optimizer):
                  initial_adafactor_decays=(0.9, 0.99, 0.999), concat_weights=True, make_separate_weights=False,
                  split_weights=False, weight_decay=0.0, clip_grad=False, mup_lrs=None,
                  hf_key_rnn="Pauljanson002/VeLO_RNN", hf_key_mlp="Pauljanson002/VeLO_MLP", legacy=False,
-                 rnn: VeLORNN = None, mlp: VeLOMLP = None):
+                 rnn: VeLORNN = None, mlp: VeLOMLP = None, process_group=None, all_shapes=None, owned=None):
         if legacy:
             raise NotImplementedError("VeLO_CUDA(legacy=True): the reference's legacy path cannot run either "
                                       "(its processor needs arguments the step loop never passes)")
@@ -113,6 +113,15 @@ class VeLO_CUDA(Optimizer):
         self._B = int(sd["rnn_to_controls.weight"].shape[0])
         if self._bank.shape != (self._B, 159) or sd["mix_layer2.weight"].shape[1] != 30:
             raise ValueError("VeLO_CUDA kernels are built for 30 LSTM inputs and the 30-4-4-3 per-element network")
+        # Sharded use (one process per GPU, each owning whole tensors): `all_shapes` lists the shapes of ALL
+        # tensors of the model in their global order, `owned` the global positions of the tensors passed
+        # to this instance (same order).  The LSTM sees every tensor (it pools over them, VeLO_RNN.py:129-131),
+        # so the per-tensor LSTM inputs are summed over the ranks and every rank runs the small LSTM itself.
+        self._pg = process_group
+        self._all_shapes = [tuple(s) for s in all_shapes] if all_shapes is not None else None
+        self._owned = list(owned) if owned is not None else None
+        if (self._all_shapes is None) != (self._owned is None):
+            raise ValueError("VeLO_CUDA: pass all_shapes and owned together")
         self._plan = None
         g0 = self.param_groups[0]
         self._w_m, self._w_f = one_minus(g0["initial_momentum_decays"]), one_minus(g0["initial_adafactor_decays"])
@@ -150,6 +159,14 @@ class VeLO_CUDA(Optimizer):
                     rank = sum(1 for d in shape if d > 1)
                     st["rank_onehot"] = F.one_hot(torch.tensor(rank), num_classes=5).float().to(dev)
                 layer_idx += 1
+        if self._owned is not None:
+            if len(self._owned) != layer_idx:
+                raise ValueError("VeLO_CUDA: `owned` must name one global position per parameter")
+            for group in self.param_groups:
+                for p in group["params"]:
+                    if p.requires_grad is not False:
+                        self.state[p]["layer_idx"] = self._owned[self.state[p]["layer_idx"]]
+            layer_idx = len(self._all_shapes)
         self.lstm_hidden_state = (
             self.lstm_init_state[0].detach().repeat(layer_idx, 1).to(dev).contiguous(),
             self.lstm_init_state[1].detach().repeat(layer_idx, 1).to(dev).contiguous(),
@@ -182,7 +199,7 @@ class VeLO_CUDA(Optimizer):
     # ------------------------------------------------------------------ planning
     def _build_plan(self, plist):
         dev = self.device
-        T = len(plist)
+        T = len(self._all_shapes) if self._all_shapes is not None else len(plist)
         H, B = self._H, self._B
         f32 = dict(dtype=torch.float32, device=dev)
         buf = {
@@ -192,14 +209,17 @@ class VeLO_CUDA(Optimizer):
             "rank": torch.stack([self.state[p]["rank_onehot"] for p in plist]).contiguous(),
             "loss": torch.zeros(1, **f32),
         }
+        layers = [self.state[p]["layer_idx"] for p in plist]
+        buf["layer_of"] = torch.tensor(layers, dtype=torch.int32, device=dev)
         tensors = []
         for i, p in enumerate(plist):
             require_cuda_param(p, "VeLO_CUDA")
             st = self.state[p]
-            if st["layer_idx"] != i:
+            li = st["layer_idx"]
+            if self._owned is None and li != i:
                 raise RuntimeError("VeLO_CUDA: every parameter needs a gradient on every step")
             fd = factored_dims_velo(tuple(p.shape))
-            common = dict(p=p.data, m=st["mom"], v=st["rms"], fdims=fd, w=buf["weights"][i], lr_mult=buf["lr_mult"][i:i + 1])
+            common = dict(p=p.data, m=st["mom"], v=st["rms"], fdims=fd, w=buf["weights"][li], lr_mult=buf["lr_mult"][li:li + 1])
             if fd is not None:
                 tensors.append(LoTensor(fac_r=st["fac_vec_row"], fac_c=st["fac_vec_col"], rcm_axis=fd[0] + 1, **common))
             else:
@@ -275,9 +295,15 @@ class VeLO_CUDA(Optimizer):
 
         h, c = self.lstm_hidden_state
         r.h, r.c = h.data_ptr(), c.data_ptr()
-        L.check(L.lib.pylo_b200_velo_tensor_features(plan.desc.ptr, plan.n_tensors, buf["rank"].data_ptr(),
-                                                     buf["fraction9"].data_ptr(), buf["loss9"].data_ptr(),
-                                                     buf["x_in"].data_ptr(), stream), "velo_tensor_features")
+        sharded = self._owned is not None
+        if sharded:
+            buf["x_in"].zero_()
+        L.check(L.lib.pylo_b200_velo_tensor_features(plan.desc.ptr, plan.n_tensors, buf["layer_of"].data_ptr(), int(r.T),
+                                                     buf["rank"].data_ptr(), buf["fraction9"].data_ptr(),
+                                                     buf["loss9"].data_ptr(), buf["x_in"].data_ptr(), stream),
+                "velo_tensor_features")
+        if sharded and torch.distributed.is_initialized() and torch.distributed.get_world_size(self._pg) > 1:
+            torch.distributed.all_reduce(buf["x_in"], group=self._pg)
         L.check(L.lib.pylo_b200_velo_rnn(C.byref(r), stream), "velo_rnn")
         plan.run_back(prm, stream)
         for group in self.param_groups:

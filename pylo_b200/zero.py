@@ -116,3 +116,24 @@ class ShardedStep:
         if self.world == 1:
             return None
         return dist.all_gather_into_tensor(self.flat, self.my_region(), group=self.pg, async_op=async_op)
+
+
+def sharded_optimizer(cls, shard: ShardedStep, **kwargs):
+    """Build ``cls`` over the tensors this rank owns, wired for the exchanges its family needs.
+
+    * CELO2 / ELO_CELO2 / ELO with ``clip_grad``: the global gradient norm is the sum over ranks
+      (one scalar all-reduce per step).
+    * VeLO: the per-tensor LSTM inputs of all tensors are summed over ranks ([T, 30] floats) and every
+      rank runs the LSTM for all T tensors; pass the same ``loss`` on every rank.
+    * AdafacLO needs nothing.
+    Call ``shard.gather()`` after ``optimizer.step()``.
+    """
+    params = [shard.params[i] for i in shard.owned]
+    if cls.__name__ == "VeLO_CUDA":
+        shapes = [tuple(p.shape) for p in shard.params]
+        return cls(params, process_group=shard.pg, all_shapes=shapes, owned=shard.owned, **kwargs)
+    opt = cls(params, **kwargs)
+    if hasattr(opt, "_sharded"):
+        opt._sharded = shard.world > 1
+        opt.process_group = shard.pg
+    return opt

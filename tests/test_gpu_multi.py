@@ -1,0 +1,100 @@
+"""Two ranks on two GPUs: the sharded step (whole-tensor ownership + parameter all-gather) gives the same
+parameters as one process that owns everything.  Skipped when fewer than two GPUs are visible."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import cases
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(96, 64), (64,), (64, 160), (160,), (40, 40), (8, 6, 5), (40,)]
+CASE = dict(shapes=SHAPES, init_seed=21, init_scale=0.05, grad_seed=22, grad_scale=0.2)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _build(family, params_or_shard, sharded):
+    from pylo_b200 import models, optim
+    from pylo_b200.zero import sharded_optimizer
+
+    torch.manual_seed(0)
+    if family == "adafaclo":
+        cls, kw = optim.AdafacLO_CUDA, dict(lr=1e-2, network=models.MetaMLP(39, 32, 1))
+    elif family == "elo_celo2":
+        cls, kw = optim.ELO_CELO2_CUDA, dict(lr=1e-2, network=models.CELO2MLP())   # clip_grad on by default
+    else:
+        rnn, mlp = models.VeLORNN(lstm_hidden_size=32), models.VeLOMLP()
+        with torch.no_grad():
+            for name, p in mlp.named_parameters():
+                if name.endswith("_") or "_." in name:
+                    p.mul_(0.05)
+        cls, kw = optim.VeLO_CUDA, dict(lr=10.0, num_steps=100, rnn=rnn, mlp=mlp)
+    return sharded_optimizer(cls, params_or_shard, **kw) if sharded else cls(params_or_shard, **kw)
+
+
+def _worker(rank, world, port, family, out):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from pylo_b200.zero import ShardedStep
+
+        loss = lambda t: torch.tensor(cases.velo_loss(t), device=dev)
+        # sharded run
+        params = [torch.nn.Parameter(v.to(dev)) for v in cases.init_values(CASE)]
+        shard = ShardedStep(params)
+        opt = _build(family, shard, True)
+        for t in (1, 2, 3):
+            grads = cases.grads_at(CASE, t)
+            for i in shard.owned:
+                params[i].grad = grads[i].to(dev)
+            opt.step(loss(t)) if family == "velo" else opt.step()
+            shard.gather()
+        torch.cuda.synchronize()
+        # the same three steps with everything on this rank
+        ref = [torch.nn.Parameter(v.to(dev)) for v in cases.init_values(CASE)]
+        opt1 = _build(family, ref, False)
+        for t in (1, 2, 3):
+            for p, g in zip(ref, cases.grads_at(CASE, t)):
+                p.grad = g.to(dev)
+            opt1.step(loss(t)) if family == "velo" else opt1.step()
+        torch.cuda.synchronize()
+        worst = max(float((a.detach() - b.detach()).abs().max()) for a, b in zip(params, ref))
+        moved = max(float((b.detach().cpu() - v).abs().max()) for b, v in zip(ref, cases.init_values(CASE)))
+        out.put((rank, "ok" if worst <= 1e-6 * max(1.0, moved / 1e-3) and moved > 0 else f"diff {worst} moved {moved}"))
+    except Exception as e:  # pragma: no cover
+        import traceback
+
+        out.put((rank, traceback.format_exc()[-600:]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("family", ["adafaclo", "elo_celo2", "velo"])
+def test_two_rank_sharded_step_matches_single_process(family):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, family, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results
