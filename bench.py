@@ -50,6 +50,7 @@ def parse():
     ap.add_argument("--optimizer", default="adafaclo", choices=sorted(STEP_BYTES))
     ap.add_argument("--layers", type=int, default=None, help="llama3_8b only: number of transformer layers (default 32)")
     ap.add_argument("--no-orthogonalize", action="store_true", help="celo2 family: skip Newton-Schulz")
+    ap.add_argument("--blocks", type=int, default=4, help="N>1: stages whose parameter all-gathers overlap the next stage")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-steps", type=int, default=3)
@@ -85,26 +86,29 @@ def seeded_networks(kind):
     return rnn, mlp
 
 
-def build_optimizer(args, shard, params, is_embedding=None):
+def is_embedding_shape(shape):
+    """Token embedding / lm head: routed to the AdamW branch in the CELO2 family."""
+    return len(shape) == 2 and shape[0] > 32768
+
+
+def build_optimizer(args, shard, params):
     from pylo_b200 import optim
 
     k = args.optimizer
-    if k == "adafaclo":
-        return optim.AdafacLO_CUDA(params, lr=1e-3, step_mult=0.01, exp_mult=0.001, network=seeded_networks(k))
-    if k == "elo":
-        opt = optim.ELO_CUDA(params, lr=1e-3, weight_decay=0.1, clip_grad=True, network=seeded_networks(k))
-    elif k in ("celo2", "elo_celo2"):
-        groups = [{"params": [p for p, e in zip(params, is_embedding) if not e]},
-                  {"params": [p for p, e in zip(params, is_embedding) if e], "is_embedding": True}]
-        groups = [g for g in groups if g["params"]]
-        cls = optim.CELO2_CUDA if k == "celo2" else optim.ELO_CELO2_CUDA
-        kw = dict(lr=1e-3, weight_decay=0.1, orthogonalize=not args.no_orthogonalize, network=seeded_networks(k))
-        opt = cls(groups, **kw)
-    else:
+    if k == "velo":
         rnn, mlp = seeded_networks(k)
         return optim.VeLO_CUDA(params, lr=1e-3, num_steps=10000, rnn=rnn, mlp=mlp, process_group=shard.pg,
                                all_shapes=[tuple(p.shape) for p in shard.params], owned=shard.owned)
+    if k == "adafaclo":
+        opt = optim.AdafacLO_CUDA(shard.param_groups(), lr=1e-3, step_mult=0.01, exp_mult=0.001, network=seeded_networks(k))
+    elif k == "elo":
+        opt = optim.ELO_CUDA(shard.param_groups(), lr=1e-3, weight_decay=0.1, clip_grad=True, network=seeded_networks(k))
+    else:
+        cls = optim.CELO2_CUDA if k == "celo2" else optim.ELO_CELO2_CUDA
+        opt = cls(shard.param_groups(is_embedding_shape), lr=1e-3, weight_decay=0.1,
+                  orthogonalize=not args.no_orthogonalize, network=seeded_networks(k))
     opt._sharded, opt.process_group = shard.world > 1, shard.pg
+    opt.after_group = shard.after_group
     return opt
 
 
@@ -210,7 +214,7 @@ def config_of(args, shapes, n_gpus):
         "orthogonalize": (not args.no_orthogonalize) if "celo2" in args.optimizer else None,
         "cache": "inputs larger than L2 (no flush needed)" if W.total_params(shapes) * 24 / max(n_gpus, 1) > 2e9
                  else "L2 flushed between steps by writing a 512 MiB buffer",
-        "parallelism": f"zero1x{n_gpus}",
+        "parallelism": f"zero1x{n_gpus}", "gather_blocks": (args.blocks if n_gpus > 1 and args.optimizer != "velo" else 1),
     }
 
 
@@ -236,7 +240,7 @@ def run_b200(args):
     import torch.distributed as dist
 
     from pylo_b200 import workloads as W
-    from pylo_b200.zero import ShardedStep
+    from pylo_b200.zero import ShardedStep, StagedShardedStep
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -256,14 +260,16 @@ def run_b200(args):
     if need > free * 0.97:
         raise SystemExit(f"workload needs ~{need / 1e9:.0f} GB per GPU, {free / 1e9:.0f} GB free: refusing to run")
 
-    shard = ShardedStep.from_shapes(shapes, dev, init_scale=0.02, seed=1)
+    if args.optimizer == "velo":  # its LSTM needs every tensor's statistics before any tensor is applied
+        shard = ShardedStep.from_shapes(shapes, dev, init_scale=0.02, seed=1)
+    else:
+        shard = StagedShardedStep(shapes, dev, blocks=args.blocks, init_scale=0.02, seed=1)
     owned = shard.owned
     params = [shard.params[i] for i in owned]
     pool = W.make_grad_pool([shapes[i] for i in owned], gscale, dev, seed=2 + rank, kind=gkind)
     for p in params:
         p.grad = pool[tuple(p.shape)]
-    emb = [shapes[i][0] > 32768 for i in owned]  # token embedding / lm head go to the AdamW branch in the CELO2 family
-    opt = build_optimizer(args, shard, params, emb)
+    opt = build_optimizer(args, shard, params)
     owned_n = sum(p.numel() for p in params)
     velo = args.optimizer == "velo"
     loss = torch.tensor(1.0, device=dev)
@@ -274,8 +280,12 @@ def run_b200(args):
     def one_step():
         if flush is not None:
             flush.fill_(1)
-        opt.step(loss) if velo else opt.step()
-        shard.gather()
+        if velo:
+            opt.step(loss)
+            shard.gather()
+        else:
+            opt.step()       # starts each block's all-gather as soon as the block's kernels are enqueued
+            shard.finish()
 
     def barrier():
         torch.cuda.synchronize()

@@ -52,6 +52,7 @@ class _AdafacFamily(Optimizer):
         self._gnorm = None
         self.process_group = None   # set (or set _sharded) when the tensors of the model are split over ranks
         self._sharded = False
+        self.after_group = None     # optional callable(group index), called once a param group's kernels are enqueued
         # fp32 values of 1 - beta, read back once (the reference evaluates them on the device every step)
         self._w_m, self._w_f = one_minus(self.beta_m), one_minus(self.beta_adafactor)
         self._w_v = one_minus(self.beta_rms)[0]
@@ -118,6 +119,8 @@ class _AdafacFamily(Optimizer):
         plan.refresh([p.grad for p in plist], steps=steps)
         plan.run_front(prm, stream)
         plan.run_back(prm, stream)
+        if self.after_group is not None:
+            self.after_group(gi)
 
     def _params_struct(self, gnorm_ptr, wd_mode, nan_to_num):
         prm = L.StepParams()

@@ -74,6 +74,7 @@ class _Celo2Family(Optimizer):
         self._gnorm = None
         self.process_group = None   # set (or set _sharded) when the tensors of the model are split over ranks
         self._sharded = False
+        self.after_group = None     # optional callable(group index), called once a param group's kernels are enqueued
         # fp32 values of 1 - beta, read back once (the reference evaluates them on the device every step)
         self._w_m, self._w_f = one_minus(self.beta_m), one_minus(self.beta_fac)
         self._w_v = float(1 - self.beta_rms[-1])
@@ -256,6 +257,8 @@ class _Celo2Family(Optimizer):
                 L.check(L.lib.pylo_b200_adamw(adam.table.ptr, adam.tiles.ptr, adam.n_tiles, int(not self._shared_adam),
                                               b1, 1 - b1, b2, 1 - b2, eps, C.byref(prm), stream), "adamw")
                 self._keepg = keepg
+            if self.after_group is not None:
+                self.after_group(gi)
         return loss
 
 

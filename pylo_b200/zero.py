@@ -58,6 +58,47 @@ def flat_layout(shapes: Sequence[Tuple[int, ...]], owner: Sequence[int], world_s
     return offsets, shard
 
 
+def partition_blocks(shapes: Sequence[Tuple[int, ...]], world_size: int, blocks: int,
+                     cost: Optional[Callable[[Tuple[int, ...]], float]] = None):
+    """Owner rank and block of every tensor, for a step that is cut into ``blocks`` stages.
+
+    Tensors are first balanced over the ranks (as :func:`partition`), then each rank's tensors over its
+    blocks; the buffer is laid out ``[block][rank][tensors | pad]`` so that the parameters a stage updates
+    form, over all ranks, one contiguous range that a single all-gather can fill while the next stage
+    computes.  Returns (owner, block, offsets, subs) with ``subs[b]`` the size of one rank's cell in block b.
+    """
+    cost = cost or (lambda s: float(_numel(s)))
+    owner = partition(shapes, world_size, cost)
+    block = [0] * len(shapes)
+    sizes = [(_numel(s) + ALIGN - 1) // ALIGN * ALIGN for s in shapes]
+    per_rank = max(sum(sz for sz, o in zip(sizes, owner) if o == r) for r in range(world_size))
+    # block capacities are the same on every rank: the first block is as large as the largest tensor
+    # needs (a tensor cannot be split), the rest share what remains
+    first = max(max(sizes), -(-per_rank // blocks))
+    rest = -(-max(per_rank - first, 0) // max(blocks - 1, 1))
+    caps = [first] + [rest] * (blocks - 1)
+    for r in range(world_size):
+        mine = sorted((i for i, o in enumerate(owner) if o == r), key=lambda i: (-sizes[i], i))
+        fill = [0] * blocks
+        for i in mine:  # first fit, largest first; what fits nowhere goes to the emptiest block
+            fits = [b for b in range(blocks) if fill[b] + sizes[i] <= caps[b]]
+            bsel = fits[0] if fits else min(range(blocks), key=lambda b: (fill[b] - caps[b], b))
+            block[i] = bsel
+            fill[bsel] += sizes[i]
+    used = {}
+    local = [0] * len(shapes)
+    for i, s in enumerate(shapes):
+        key = (block[i], owner[i])
+        local[i] = used.get(key, 0)
+        used[key] = local[i] + (_numel(s) + ALIGN - 1) // ALIGN * ALIGN
+    subs = [max([used.get((b, r), 0) for r in range(world_size)] + [ALIGN]) for b in range(blocks)]
+    base = [0] * blocks
+    for b in range(1, blocks):
+        base[b] = base[b - 1] + subs[b - 1] * world_size
+    offsets = [base[block[i]] + owner[i] * subs[block[i]] + local[i] for i in range(len(shapes))]
+    return owner, block, offsets, subs
+
+
 class ShardedStep:
     """Flat parameter buffer + ownership + the post-step gather for one process group.
 
@@ -116,6 +157,88 @@ class ShardedStep:
         if self.world == 1:
             return None
         return dist.all_gather_into_tensor(self.flat, self.my_region(), group=self.pg, async_op=async_op)
+
+
+class StagedShardedStep:
+    """Sharded step cut into stages whose parameter all-gathers overlap the next stage's kernels.
+
+    The tensors a rank owns are split into ``blocks`` groups; build the optimizer with
+    :meth:`param_groups` (one param group per block - the optimizer classes run their param groups one
+    after the other) and attach :meth:`after_group` as the optimizer's ``after_group`` hook.  After the
+    kernels of block b are enqueued, the all-gather of block b starts on a second stream while block
+    b+1 computes; :meth:`finish` joins the streams at the end of the step.
+    """
+
+    def __init__(self, shapes: Sequence[Tuple[int, ...]], device, blocks: int = 4, init_scale: float = 0.02,
+                 seed: int = 1, process_group=None, cost=None):
+        self.pg = process_group
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+        self.blocks = blocks if self.world > 1 else 1
+        shapes = [tuple(s) for s in shapes]
+        self.owner, self.block, self.offsets, self.subs = partition_blocks(shapes, self.world, self.blocks, cost)
+        self.base = [sum(self.subs[:b]) * self.world for b in range(self.blocks)]
+        self.flat = torch.zeros(sum(self.subs) * self.world, dtype=torch.float32, device=device)
+        gen = torch.Generator(device=device)
+        self.params = []
+        for i, (off, s) in enumerate(zip(self.offsets, shapes)):
+            view = self.flat[off:off + _numel(s)].view(s)
+            gen.manual_seed(seed * 1000003 + i)
+            view.normal_(0.0, init_scale, generator=gen)
+            self.params.append(torch.nn.Parameter(view, requires_grad=True))
+        self.owned = [i for i, r in enumerate(self.owner) if r == self.rank]
+        self.shard = sum(self.subs)
+        self._comm = torch.cuda.Stream(device=device) if self.world > 1 else None
+        self._works = []
+
+    def param_groups(self, is_embedding=None):
+        """Param groups in block order: one per block, or two (ordinary tensors, then embedding-like
+        ones flagged ``is_embedding=True`` for the CELO2 family) when ``is_embedding(shape)`` is given."""
+        out, info = [], []
+        for b in range(self.blocks):
+            mine = [self.params[i] for i in self.owned if self.block[i] == b]
+            if is_embedding is None:
+                parts = [({}, mine)]
+            else:
+                parts = [({}, [p for p in mine if not is_embedding(tuple(p.shape))]),
+                         ({"is_embedding": True}, [p for p in mine if is_embedding(tuple(p.shape))])]
+            parts = [(extra, ps) for extra, ps in parts if ps]
+            for k, (extra, ps) in enumerate(parts):
+                out.append(dict(params=ps, **extra))
+                info.append((b, k == len(parts) - 1))
+        self._group_info = info
+        return out
+
+    def after_group(self, gi: int):
+        """Hook for the optimizer: param group ``gi`` is enqueued; when it closes a block, start that
+        block's all-gather."""
+        if self.world == 1:
+            return
+        b, closes = self._group_info[gi]
+        if not closes:
+            return
+        ev = torch.cuda.Event()
+        ev.record()
+        sub = self.subs[b]
+        block = self.flat[self.base[b]:self.base[b] + self.world * sub]
+        mine = block[self.rank * sub:(self.rank + 1) * sub]
+        with torch.cuda.stream(self._comm):
+            self._comm.wait_event(ev)
+            self._works.append(dist.all_gather_into_tensor(block, mine, group=self.pg, async_op=True))
+
+    def finish(self):
+        """Make the current stream wait for every gather of this step."""
+        for w in self._works:
+            w.wait()
+        self._works = []
+
+    def gather(self):
+        """Non-overlapped fallback: gather every block now (used when no hook was attached)."""
+        if self.world == 1:
+            return
+        for gi in range(len(self._group_info)):
+            self.after_group(gi)
+        self.finish()
 
 
 def sharded_optimizer(cls, shard: ShardedStep, **kwargs):

@@ -84,6 +84,64 @@ def _worker(rank, world, port, family, out):
         dist.destroy_process_group()
 
 
+def _staged_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from pylo_b200 import models, optim
+        from pylo_b200.zero import StagedShardedStep
+
+        shapes = SHAPES + [(72, 48), (48, 72), (30, 200)]
+        case = dict(CASE, shapes=shapes)
+        shard = StagedShardedStep(shapes, dev, blocks=3, init_scale=0.05, seed=4)
+        start = [p.detach().clone() for p in shard.params]
+        torch.manual_seed(0)
+        opt = optim.AdafacLO_CUDA(shard.param_groups(), lr=1e-2, network=models.MetaMLP(39, 32, 1))
+        opt.after_group = shard.after_group
+        for t in (1, 2, 3):
+            grads = cases.grads_at(case, t)
+            for i in shard.owned:
+                shard.params[i].grad = grads[i].to(dev)
+            opt.step()
+            shard.finish()
+        torch.cuda.synchronize()
+        ref = [torch.nn.Parameter(v.clone()) for v in start]
+        torch.manual_seed(0)
+        opt1 = optim.AdafacLO_CUDA(ref, lr=1e-2, network=models.MetaMLP(39, 32, 1))
+        for t in (1, 2, 3):
+            for p, g in zip(ref, cases.grads_at(case, t)):
+                p.grad = g.to(dev)
+            opt1.step()
+        torch.cuda.synchronize()
+        same = all(torch.equal(a.detach(), b.detach()) for a, b in zip(shard.params, ref))
+        moved = any(not torch.equal(a.detach(), b) for a, b in zip(ref, start))
+        out.put((rank, "ok" if same and moved else f"same={same} moved={moved}"))
+    except Exception:  # pragma: no cover
+        import traceback
+
+        out.put((rank, traceback.format_exc()[-600:]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_staged_step_with_overlapped_gathers_is_bit_identical():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_staged_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results
+
+
 @pytest.mark.parametrize("family", ["adafaclo", "elo_celo2", "velo"])
 def test_two_rank_sharded_step_matches_single_process(family):
     if torch.cuda.device_count() < 2:

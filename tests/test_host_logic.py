@@ -72,6 +72,23 @@ def test_partition_is_deterministic_balanced_and_total(world):
     assert all(o * shard <= off < (o + 1) * shard for off, o in zip(offsets, owner))
 
 
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("wl", ["llama3_8b", "gpt2_medium"])
+def test_block_layout_keeps_gather_ranges_contiguous_and_tight(world, wl):
+    shapes = workloads.WORKLOADS[wl]()
+    blocks = 4
+    owner, block, offsets, subs = zero.partition_blocks(shapes, world, blocks)
+    total = workloads.total_params(shapes)
+    spans = sorted((off, off + workloads.numel(s)) for off, s in zip(offsets, shapes))
+    assert all(a1 <= b0 for (_, a1), (b0, _) in zip(spans, spans[1:])), "tensors overlap"
+    base = [sum(subs[:b]) * world for b in range(blocks)]
+    for off, s, o, b in zip(offsets, shapes, owner, block):
+        lo = base[b] + o * subs[b]
+        assert lo <= off and off + workloads.numel(s) <= lo + subs[b], "tensor outside its (block, rank) cell"
+    if wl == "llama3_8b":
+        assert sum(subs) * world < 1.01 * total  # indivisible 525 M-element tensors must not inflate the buffer
+
+
 def test_workload_sizes():
     assert workloads.total_params(workloads.mlp_784()) == 118282
     assert workloads.total_params(workloads.celo2_4096()) == 4096 * 4096 + 4096
