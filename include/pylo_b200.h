@@ -219,8 +219,8 @@ int pylo_b200_apply(const pylo_tensor_desc* descs, const pylo_tile* tiles, int n
 
 /* Phase C for the FAST2D tensors of the ADAFAC family (same arithmetic as pylo_b200_apply, organised for
  * the FMA-bound 39-32-32-2 network: a thread keeps one column, packed fp32x2 FMAs).  ctiles: one entry per
- * tile with strip = row-tile index, cb = column-tile index, pad_ = columns per CTA (32, 64, 128 or 256); a tile
- * has 16 rows at 256 columns and 32 rows otherwise.  With this kernel in use pylo_b200_apply gets only the non-FAST2D tiles.
+ * tile with strip = row-tile index, cb = column-tile index, pad_ = columns per CTA (32, 64, 128 or 256) | (n_sub << 16); a work item
+ * covers n_sub sub-tiles of 32 rows in one column block.  With this kernel in use pylo_b200_apply gets only the non-FAST2D tiles.
  * With one of the FAST2D kernels in use pylo_b200_apply handles the GENERIC and VEC1D units only. */
 int pylo_b200_apply_adafac_cols(const pylo_tensor_desc* descs, const pylo_atile* ctiles, int n_ctiles,
                                 const pylo_step_params* prm, void* stream);

@@ -52,7 +52,8 @@ struct Fold {
   static constexpr int W3 = B2 + F::H;            // [H][2], k-major (only direction and magnitude)
   static constexpr int B3 = W3 + F::H * 2;        // [2]
   static constexpr int SC = B3 + 2;               // [0] param_scale (VeLO), [1] lr_eff
-  static constexpr int SIZE = SC + 2;
+  static constexpr int W3P = SC + 2;              // [H/2][4]: (dir[2j], dir[2j+1], mag[2j], mag[2j+1]) for packed dot products
+  static constexpr int SIZE = W3P + 2 * F::H;
 };
 static_assert(Fold<PYLO_FAM_ADAFAC>::SIZE <= PYLO_WFOLD_STRIDE, "wfold too small");
 
@@ -75,6 +76,14 @@ __device__ __forceinline__ float lerp_torch(float a, float b, float w) {
 }
 
 __device__ __forceinline__ float safe_rsqrt(float x) { return rsqrtf(fmaxf(x, 1e-9f)); }
+
+// rsqrt of a value known to be a positive normal number (v + eps with eps >= 1e-8): the bare
+// hardware approximation (about 1.5 ulp), without the range fix-ups rsqrtf() carries
+__device__ __forceinline__ float rsqrt_pos(float x) {
+  float y;
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ float grad_scale_of(const pylo_tensor_desc& d, const pylo_step_params& prm) {
   if (d.clip_norm <= 0.0f || prm.gnorm_sq == nullptr) return 1.0f;

@@ -555,6 +555,10 @@ __global__ void __launch_bounds__(NT) k_prep_apply(const pylo_tensor_desc* __res
       o[L::W3 + e] = (FAM == PYLO_FAM_CELO2) ? w[o_w3 + k * F::NOUT + q] : w[o_w3 + q * H + k];
     }
     if (tid < 2) o[L::B3 + tid] = w[o_b3 + tid];
+    for (int e = tid; e < H * 2; e += NT) {  // pair-major copy of the output layer
+      const int jp = e / 4, r = e % 4, k = 2 * jp + (r & 1), q = r >> 1;
+      o[L::W3P + e] = (FAM == PYLO_FAM_CELO2) ? w[o_w3 + k * F::NOUT + q] : w[o_w3 + q * H + k];
+    }
     if (tid == 0) {
       // VeLO: param_scale = sqrt(mean(p^2) + 1e-9) from the p feature's sum (velo_kernel.cu:297)
       o[L::SC + 0] = (FAM == PYLO_FAM_VELO) ? sqrtf(d.sums[2] / (float)d.n + 1e-9f) : 1.0f;
@@ -765,7 +769,7 @@ __global__ void __launch_bounds__(NT) k_apply(const pylo_tensor_desc* __restrict
 //     layer can run as a short loop over k instead of 1000+ unrolled instructions;
 //   * the next pair's operands are loaded while the current pair is computed.
 // ================================================================================================
-#define CC_TILE_ROWS 32   // rows per tile when a CTA is narrower than 256 columns (16 rows at 256 columns)
+#define CC_TILE_ROWS 32   // rows per tile
 
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
   uint64_t r;
@@ -822,11 +826,12 @@ __global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const 
     const pylo_atile ct = ctiles[t];
     const pylo_tensor_desc& d = descs[ct.tensor];
     const int X = d.X, Y = d.Y;
-    const int cw = ct.pad_;                          // columns per CTA: 32, 64, 128 or 256
+    const int cw = ct.pad_ & 0xffff;                 // columns per CTA: 32, 64, 128 or 256
+    const int n_sub = ct.pad_ >> 16;                 // the work item covers n_sub sub-tiles of CC_TILE_ROWS rows
     const int ng = NT / cw;                          // row groups
-    const int rt = cw == NT ? 16 : CC_TILE_ROWS;     // rows per tile
-    const int rows_per_thread = rt / ng;             // 16, 16, 8 or 4
-    const int x0 = ct.strip * rt, y0 = ct.cb * cw;
+    const int rt = CC_TILE_ROWS;                     // rows per sub-tile
+    const int rows_per_thread = rt / ng;             // 32, 16, 8 or 4
+    const int y0 = ct.cb * cw;
     const int col = tid % cw, rg = tid / cw;
     const int y = y0 + col;
     const bool colok = y < Y;
@@ -836,6 +841,24 @@ __global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const 
       for (int e = tid; e < L::SIZE; e += NT) sm.w[e] = d.wfold[e];
       loaded = ct.tensor;
     }
+    // this column's first-layer term (stored transposed, [32][Y]); each thread keeps its own slot, and it
+    // serves every sub-tile of the work item
+#pragma unroll 4
+    for (int j = 0; j < 16; ++j) {
+      sm.hb[j][tid][0] = d.h_b[(int64_t)(2 * j) * Y + yc];
+      sm.hb[j][tid][1] = d.h_b[(int64_t)(2 * j + 1) * Y + yc];
+    }
+    const float fb0 = d.f_b[yc], fb1 = d.f_b[Y + yc], fb2 = d.f_b[2 * (int64_t)Y + yc];
+    const float gs = grad_scale_of(d, prm);
+    const int64_t n = d.n;
+    const float* __restrict__ gp = d.g;
+    float* __restrict__ pp = d.p;
+    const float* __restrict__ mp = d.m;
+    const float* __restrict__ vp = d.v;
+    for (int sub = 0; sub < n_sub; ++sub) {
+    const int x0 = (ct.strip * n_sub + sub) * rt;
+    if (x0 >= X) break;
+    __syncthreads();  // the previous sub-tile's rows are no longer read
     for (int e = tid; e < rt * 32; e += NT) {
       const int r = e >> 5, x = x0 + r;
       sm.ha[r][e & 31] = x < X ? d.h_a[(int64_t)x * 32 + (e & 31)] : 0.f;
@@ -844,22 +867,8 @@ __global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const 
       const int r = e >> 2, x = x0 + r;
       sm.fx[r][e & 3] = x < X ? d.fx[(int64_t)x * 4 + (e & 3)] : 0.f;
     }
-    // this column's first-layer term (stored transposed, [32][Y]); each thread keeps its own slot
-#pragma unroll 4
-    for (int j = 0; j < 16; ++j) {
-      sm.hb[j][tid][0] = d.h_b[(int64_t)(2 * j) * Y + yc];
-      sm.hb[j][tid][1] = d.h_b[(int64_t)(2 * j + 1) * Y + yc];
-    }
     __syncthreads();
-    const float fb0 = d.f_b[yc], fb1 = d.f_b[Y + yc], fb2 = d.f_b[2 * (int64_t)Y + yc];
-    const float gs = grad_scale_of(d, prm);
     const Fin fin = make_fin(d, 1.0f, sm.w[L::SC + 1], prm.wd_mode);
-    const int64_t n = d.n;
-    const float* __restrict__ gp = d.g;
-    float* __restrict__ pp = d.p;
-    const float* __restrict__ mp = d.m;
-    const float* __restrict__ vp = d.v;
-
     float cg[E], cp[E], cm0[E], cm1[E], cm2[E], cv[E];
     auto load_rows = [&](int q, float* g, float* p, float* m0, float* m1, float* m2, float* v) {
 #pragma unroll
@@ -884,7 +893,7 @@ __global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const 
       for (int e = 0; e < E; ++e) {
         const int r = rg + ng * (q + e);
         const float g = xform_grad(cg[e], gs, prm.clip_val, prm.nan_to_num);
-        const float rs = rsqrtf(cv[e] + prm.eps_feat);
+        const float rs = rsqrt_pos(cv[e] + prm.eps_feat);
         const float4 fa = ld4(&sm.fx[r][0]);
         elem_features<PYLO_FAM_ADAFAC>(f[e], g, cp[e], cm0[e], cm1[e], cm2[e], cv[e], rs, fa.x * fb0, fa.y * fb1, fa.z * fb2);
       }
@@ -943,58 +952,60 @@ __global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const 
           for (int e = 0; e < E; ++e) { h2[e][2 * j] = b.x; h2[e][2 * j + 1] = b.y; }
         }
       }
-#pragma unroll 2
-      for (int k = 0; k < 32; ++k) {
-        uint64_t hk[E];
-        if constexpr (E == 4) {
-          const float4 a = ld4(&sm.h1[k][tid][0]);
-          hk[0] = pack2(a.x, a.x); hk[1] = pack2(a.y, a.y); hk[E - 2] = pack2(a.z, a.z); hk[E - 1] = pack2(a.w, a.w);
-        } else {
-          const float2 a = *reinterpret_cast<const float2*>(&sm.h1[k][tid][0]);
-          hk[0] = pack2(a.x, a.x); hk[1] = pack2(a.y, a.y);
-        }
-        const ulonglong2* wrow = reinterpret_cast<const ulonglong2*>(&sm.w[L::W2 + k * 32]);
+      {
+        // the staged activations of unit k+1 are requested while unit k is multiplied in
+        float2 cur = *reinterpret_cast<const float2*>(&sm.h1[0][tid][0]);
+#pragma unroll 4
+        for (int k = 0; k < 32; ++k) {
+          const float2 nxt = *reinterpret_cast<const float2*>(&sm.h1[(k + 1) & 31][tid][0]);
+          const uint64_t hk0 = pack2(cur.x, cur.x), hk1 = pack2(cur.y, cur.y);
+          const ulonglong2* wrow = reinterpret_cast<const ulonglong2*>(&sm.w[L::W2 + k * 32]);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const ulonglong2 w = wrow[j];
-#pragma unroll
-          for (int e = 0; e < E; ++e) {
-            h2[e][2 * j] = fma2(w.x, hk[e], h2[e][2 * j]);
-            h2[e][2 * j + 1] = fma2(w.y, hk[e], h2[e][2 * j + 1]);
+          for (int j = 0; j < 8; ++j) {
+            const ulonglong2 w = wrow[j];
+            h2[0][2 * j] = fma2(w.x, hk0, h2[0][2 * j]); h2[0][2 * j + 1] = fma2(w.y, hk0, h2[0][2 * j + 1]);
+            h2[1][2 * j] = fma2(w.x, hk1, h2[1][2 * j]); h2[1][2 * j + 1] = fma2(w.y, hk1, h2[1][2 * j + 1]);
           }
+          cur = nxt;
         }
       }
-      // ---- output layer: (direction, magnitude) as one packed accumulator per row
-      const uint64_t b3 = *reinterpret_cast<const uint64_t*>(&sm.w[L::B3]);
-      uint64_t out[E];
+      // ---- output layer: direction and magnitude as packed dot products over hidden-unit pairs, two
+      //      partial accumulators each so that no dependent chain is longer than eight FMAs
+      uint64_t od[E][2], om[E][2];
 #pragma unroll
-      for (int e = 0; e < E; ++e) out[e] = b3;
+      for (int e = 0; e < E; ++e) { od[e][0] = od[e][1] = 0ull; om[e][0] = om[e][1] = 0ull; }
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(&sm.w[L::W3 + 4 * j]);  // rows 2j and 2j+1
+        const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(&sm.w[L::W3P + 4 * j]);  // (dir pair, mag pair)
 #pragma unroll
         for (int e = 0; e < E; ++e) {
           float a, b;
           unpack2(h2[e][j], a, b);
-          a = fmaxf(a, 0.f); b = fmaxf(b, 0.f);
-          out[e] = fma2(w.x, pack2(a, a), out[e]);
-          out[e] = fma2(w.y, pack2(b, b), out[e]);
+          const uint64_t r = pack2(fmaxf(a, 0.f), fmaxf(b, 0.f));
+          od[e][j & 1] = fma2(w.x, r, od[e][j & 1]);
+          om[e][j & 1] = fma2(w.y, r, om[e][j & 1]);
         }
+      }
+      float o0v[E], o1v[E];
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        float a, b, c, dd;
+        unpack2(add2(od[e][0], od[e][1]), a, b);
+        unpack2(add2(om[e][0], om[e][1]), c, dd);
+        o0v[e] = (a + b) + sm.w[L::B3];
+        o1v[e] = (c + dd) + sm.w[L::B3 + 1];
       }
 #pragma unroll
       for (int e = 0; e < E; ++e) {
         const int x = x0 + rg + ng * (q + e);
-        if (colok && x < X) {
-          float o0, o1;
-          unpack2(out[e], o0, o1);
-          pp[(int64_t)x * Y + y] = finish<PYLO_FAM_ADAFAC>(cp[e], o0, o1, fin);
-        }
+        if (colok && x < X) pp[(int64_t)x * Y + y] = finish<PYLO_FAM_ADAFAC>(cp[e], o0v[e], o1v[e], fin);
       }
       if (more) {
 #pragma unroll
         for (int e = 0; e < E; ++e) { cg[e] = ng_[e]; cp[e] = np_[e]; cm0[e] = nm0[e]; cm1[e] = nm1[e]; cm2[e] = nm2[e]; cv[e] = nv[e]; }
       }
     }
+    }  // sub-tiles
   }
 }
 

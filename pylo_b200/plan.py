@@ -257,7 +257,11 @@ class LoPlan:
             X, Y = int(tdesc["X"][i]), int(tdesc["Y"][i])
             if family == L.FAM_ADAFAC:
                 cw = min((256, 128, 64, 32), key=lambda c: ((Y + c - 1) // c * c - Y, -c))
-                rt, width, tag = (16 if cw == 256 else 32), cw, cw
+                ncol = (Y + cw - 1) // cw
+                # a work item is n_sub sub-tiles of 32 rows in one column block (the column terms are loaded
+                # once per item); as long as possible while the tensor still yields >= 8 items per SM
+                n_sub = next((k for k in (8, 4, 2) if ((X + 32 * k - 1) // (32 * k)) * ncol >= 1184), 1)
+                rt, width, tag = 32 * n_sub, cw, cw | (n_sub << 16)
             else:
                 tpr = min((256, 128, 64, 32, 16, 8), key=lambda c: ((Y + 4 * c - 1) // (4 * c) * 4 * c - Y, -c))
                 rt, width, tag = 8 * (256 // tpr), 4 * tpr, tpr
