@@ -227,7 +227,7 @@ int pylo_b200_apply_adafac_cols(const pylo_tensor_desc* descs, const pylo_atile*
 
 /* Phase C for the FAST2D tensors of the CELO2 and VELO families (same arithmetic as pylo_b200_apply, done on
  * pairs of adjacent elements with packed fp32x2 instructions).  ctiles: strip = row-tile index, cb = column-tile
- * index, pad_ = threads per row (8 .. 256, a thread owns 4 columns); a tile has 8 * (256 / pad_) rows and
+ * index, pad_ = threads per row (8 .. 256, a thread owns 4 columns); a tile has 16 * (256 / pad_) rows and
  * 4 * pad_ columns.  For these families pylo_b200_prep_apply stores desc.h_a as (v, v) pairs, [X][H][2], and
  * for every family desc.h_b transposed, [H][Y]. */
 int pylo_b200_apply_packed(const pylo_tensor_desc* descs, const pylo_atile* ctiles, int n_ctiles,

@@ -1058,7 +1058,7 @@ __device__ __forceinline__ uint64_t pk_feature(const PkBase& b) {
   else return mul2(b.k2, b.m2);
 }
 
-#define PK_ROWS 8  // rows per thread in a tile
+#define PK_ROWS 16  // rows per thread in a tile
 
 template <int FAM>
 __global__ void __launch_bounds__(NT, 2) k_apply_packed(const pylo_tensor_desc* __restrict__ descs,
@@ -1137,7 +1137,7 @@ __global__ void __launch_bounds__(NT, 2) k_apply_packed(const pylo_tensor_desc* 
       PkBase b[2];
       {
         float ge[4] = {cg.x, cg.y, cg.z, cg.w};
-        float rs[4] = {rsqrtf(cv.x + eps_feat), rsqrtf(cv.y + eps_feat), rsqrtf(cv.z + eps_feat), rsqrtf(cv.w + eps_feat)};
+        float rs[4] = {rsqrt_pos(cv.x + eps_feat), rsqrt_pos(cv.y + eps_feat), rsqrt_pos(cv.z + eps_feat), rsqrt_pos(cv.w + eps_feat)};
         float cl[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) { ge[u] = xform_grad(ge[u], gs, clip, prm.nan_to_num); cl[u] = fminf(fmaxf(ge[u], -0.1f), 0.1f); }

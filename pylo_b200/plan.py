@@ -264,7 +264,7 @@ class LoPlan:
                 rt, width, tag = 32 * n_sub, cw, cw | (n_sub << 16)
             else:
                 tpr = min((256, 128, 64, 32, 16, 8), key=lambda c: ((Y + 4 * c - 1) // (4 * c) * 4 * c - Y, -c))
-                rt, width, tag = 8 * (256 // tpr), 4 * tpr, tpr
+                rt, width, tag = 16 * (256 // tpr), 4 * tpr, tpr
             for rtile in range((X + rt - 1) // rt):
                 for ctile in range((Y + width - 1) // width):
                     ctiles.append((unit_of[i], rtile, ctile, tag))
