@@ -51,6 +51,9 @@ def parse():
     ap.add_argument("--layers", type=int, default=None, help="llama3_8b only: number of transformer layers (default 32)")
     ap.add_argument("--no-orthogonalize", action="store_true", help="celo2 family: skip Newton-Schulz")
     ap.add_argument("--blocks", type=int, default=4, help="N>1: stages whose parameter all-gathers overlap the next stage")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "staged"],
+                    help="N>1: how updated parameters reach the other ranks (peer stores fused into the apply kernels, "
+                         "or NCCL all-gathers per block)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-steps", type=int, default=3)
@@ -214,7 +217,8 @@ def config_of(args, shapes, n_gpus):
         "orthogonalize": (not args.no_orthogonalize) if "celo2" in args.optimizer else None,
         "cache": "inputs larger than L2 (no flush needed)" if W.total_params(shapes) * 24 / max(n_gpus, 1) > 2e9
                  else "L2 flushed between steps by writing a 512 MiB buffer",
-        "parallelism": f"zero1x{n_gpus}", "gather_blocks": (args.blocks if n_gpus > 1 and args.optimizer != "velo" else 1),
+        "parallelism": f"zero1x{n_gpus}", "exchange": getattr(args, "exchange_used", "none"),
+        "gather_blocks": (args.blocks if getattr(args, "exchange_used", "") == "staged" and args.optimizer != "velo" else 1),
     }
 
 
@@ -240,7 +244,7 @@ def run_b200(args):
     import torch.distributed as dist
 
     from pylo_b200 import workloads as W
-    from pylo_b200.zero import ShardedStep, StagedShardedStep
+    from pylo_b200.zero import FusedShardedStep, ShardedStep, StagedShardedStep
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -260,10 +264,18 @@ def run_b200(args):
     if need > free * 0.97:
         raise SystemExit(f"workload needs ~{need / 1e9:.0f} GB per GPU, {free / 1e9:.0f} GB free: refusing to run")
 
-    if args.optimizer == "velo":  # its LSTM needs every tensor's statistics before any tensor is applied
+    exchange = args.exchange
+    if exchange == "auto":
+        exchange = "fused" if args.optimizer in ("adafaclo", "elo", "velo") else "staged"
+    if world == 1:
+        exchange = "none"
+    if exchange == "fused":    # parameters reach the other ranks as peer stores from the apply kernels
+        shard = FusedShardedStep(shapes, dev, init_scale=0.02, seed=1)
+    elif args.optimizer == "velo":  # its LSTM needs every tensor's statistics before any tensor is applied
         shard = ShardedStep.from_shapes(shapes, dev, init_scale=0.02, seed=1)
-    else:
+    else:                      # NCCL all-gathers per block, overlapped with the next block's kernels
         shard = StagedShardedStep(shapes, dev, blocks=args.blocks, init_scale=0.02, seed=1)
+    args.exchange_used = exchange
     owned = shard.owned
     params = [shard.params[i] for i in owned]
     pool = W.make_grad_pool([shapes[i] for i in owned], gscale, dev, seed=2 + rank, kind=gkind)
@@ -282,7 +294,7 @@ def run_b200(args):
             flush.fill_(1)
         if velo:
             opt.step(loss)
-            shard.gather()
+            shard.gather()   # all-gather, or (fused exchange) the one-element all-reduce that orders the peer stores
         else:
             opt.step()       # starts each block's all-gather as soon as the block's kernels are enqueued
             shard.finish()

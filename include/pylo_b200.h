@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define PYLO_B200_ABI_VERSION 4
+#define PYLO_B200_ABI_VERSION 5
 
 /* optimizer families (which feature set / network geometry a launch uses) */
 #define PYLO_FAM_ADAFAC 0 /* AdafacLO_CUDA, ELO_CUDA: 28+11 features, 39-32-32-2 */
@@ -51,6 +51,7 @@ extern "C" {
 #define PYLO_TILE_ELEMS 16384 /* elements per element-wise tile */
 #define PYLO_A_COLS 1024      /* columns per row/column-sum tile */
 #define PYLO_WFOLD_STRIDE 2432 /* floats reserved per tensor for the folded network */
+#define PYLO_MAX_PEERS 7       /* other GPUs of one box */
 
 /*
  * One unit of element-wise work: a whole parameter tensor, or one matrix slice of a tensor
@@ -86,6 +87,9 @@ typedef struct pylo_tensor_desc {
   float* out;     /* CELO2: raw step output [n]; else NULL */
   const float* w; /* network weights for this tensor, family layout (see pylo_b200_prep_apply) */
   const float* lr_mult; /* VeLO: device scalar multiplying lr for this tensor, else NULL */
+  float* p_peer[PYLO_MAX_PEERS]; /* the same parameter inside the other ranks' peer-mapped buffers (first n_peer
+                                    entries valid): kernels that write p store the new value there as well, which
+                                    replaces the all-gather of updated parameters */
   int64_t n;        /* elements of this unit */
   int64_t m_stride; /* distance in floats between the three momentum planes (n for a whole tensor) */
   int64_t idx0;     /* offset of this unit's first element inside the [O,X,M,Y,I] view (0 for a whole tensor) */
@@ -103,7 +107,8 @@ typedef struct pylo_tensor_desc {
   float step;                       /* AdafacLO/ELO: 0-based step for the time features */
   float clip_norm;                  /* >0: scale g by clip_norm / max(global norm, clip_norm) */
   float exp_mult, step_mult;
-  int32_t pad_[2];
+  int32_t n_peer;                   /* number of valid p_peer entries (0: single GPU, or parameters gathered by NCCL) */
+  int32_t pad_;
 } pylo_tensor_desc;
 
 /* a unit of element-wise work: elements [start, start + PYLO_TILE_ELEMS) of tensor `tensor` */

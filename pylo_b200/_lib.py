@@ -16,7 +16,7 @@ SUMS_STRIDE = 48
 TILE_ELEMS = 16384
 A_COLS = 1024
 WFOLD_STRIDE = 2432
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 FAM_ADAFAC, FAM_CELO2, FAM_VELO = 0, 1, 2
 MODE_FAST2D, MODE_GENERIC, MODE_VEC1D = 0, 1, 2
@@ -25,14 +25,16 @@ _PTR_FIELDS = [
     "g", "p", "m", "v", "fac_a", "fac_b", "f_a", "f_b", "fx", "sum_a", "sum_b", "part_a", "part_b",
     "h_a", "h_b", "closed", "sums", "wfold", "tile_part", "out", "w", "lr_mult",
 ]
+MAX_PEERS = 7
 DESC_DTYPE = np.dtype(
     [(name, np.uint64) for name in _PTR_FIELDS]
+    + [("p_peer", np.uint64, (MAX_PEERS,))]
     + [(name, np.int64) for name in ("n", "m_stride", "idx0", "La", "Lb")]
     + [(name, np.int32) for name in (
         "O", "X", "M", "Y", "I", "mode", "r_is_a", "rcm_pre", "rcm_A", "rcm_post", "rb", "n_strips", "n_cb",
         "tile0", "n_tiles", "vec_elementwise")]
     + [(name, np.float32) for name in ("lr", "wd", "step", "clip_norm", "exp_mult", "step_mult")]
-    + [("pad_", np.int32, (2,))]
+    + [("n_peer", np.int32), ("pad_", np.int32)]
 )
 TILE_DTYPE = np.dtype([("start", np.int64), ("tensor", np.int32), ("pad_", np.int32)])
 ATILE_DTYPE = np.dtype([("tensor", np.int32), ("strip", np.int32), ("cb", np.int32), ("pad_", np.int32)])

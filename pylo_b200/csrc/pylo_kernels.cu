@@ -660,6 +660,23 @@ __device__ __forceinline__ void network(const uint32_t s_w, float (&h1)[E][Fam<F
   });
 }
 
+// The parameter's copies in the other ranks' buffers (peer-mapped memory reached by plain stores).
+// The pointers are re-read from the descriptor at every store (they sit in L1) rather than held in
+// fourteen registers; with n_peer == 0 the cost is one compare.
+struct Peers {
+  float* const* p;
+  int n;
+};
+__device__ __forceinline__ Peers load_peers(const pylo_tensor_desc& d) { return Peers{d.p_peer, d.n_peer}; }
+__device__ __forceinline__ void peer_store(const Peers& q, int64_t idx, float v) {
+#pragma unroll 1
+  for (int k = 0; k < q.n; ++k) q.p[k][idx] = v;
+}
+__device__ __forceinline__ void peer_store4(const Peers& q, int64_t idx, float4 v) {
+#pragma unroll 1
+  for (int k = 0; k < q.n; ++k) st4(q.p[k] + idx, v);
+}
+
 // per-tensor scalars of the output stage, read once per tile
 struct Fin {
   float exp_mult, step_mult, wd, lr, lr_eff, param_scale;
@@ -710,6 +727,7 @@ __global__ void __launch_bounds__(NT) k_apply(const pylo_tensor_desc* __restrict
     const int cnt = (int)min((int64_t)PYLO_TILE_ELEMS, n - start);
     const float gs = grad_scale_of(d, prm);
     const Fin fin = make_fin(d, s_w[L::SC], s_w[L::SC + 1], prm.wd_mode);
+    const Peers peers = load_peers(d);
     const float* gp = d.g + start;
     float* pp = d.p + start;
     float* op = (FAM == PYLO_FAM_CELO2) ? d.out + start : pp;
@@ -748,7 +766,9 @@ __global__ void __launch_bounds__(NT) k_apply(const pylo_tensor_desc* __restrict
 #pragma unroll
         for (int j = 0; j < H; ++j) h1[0][j] = s_w[L::B1 + j];
         network<FAM, true, 1>(s_wa, h1, f, o0, o1);
-        op[i] = finish<FAM>(p, o0[0], o1[0], fin);
+        const float pn = finish<FAM>(p, o0[0], o1[0], fin);
+        op[i] = pn;
+        if (FAM != PYLO_FAM_CELO2) peer_store(peers, start + i, pn);
       }
     }
   }
@@ -855,6 +875,7 @@ __global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const 
     float* __restrict__ pp = d.p;
     const float* __restrict__ mp = d.m;
     const float* __restrict__ vp = d.v;
+    const Peers peers = load_peers(d);
     for (int sub = 0; sub < n_sub; ++sub) {
     const int x0 = (ct.strip * n_sub + sub) * rt;
     if (x0 >= X) break;
@@ -998,7 +1019,11 @@ __global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const 
 #pragma unroll
       for (int e = 0; e < E; ++e) {
         const int x = x0 + rg + ng * (q + e);
-        if (colok && x < X) pp[(int64_t)x * Y + y] = finish<PYLO_FAM_ADAFAC>(cp[e], o0v[e], o1v[e], fin);
+        if (colok && x < X) {
+          const float pn = finish<PYLO_FAM_ADAFAC>(cp[e], o0v[e], o1v[e], fin);
+          pp[(int64_t)x * Y + y] = pn;
+          peer_store(peers, (int64_t)x * Y + y, pn);
+        }
       }
       if (more) {
 #pragma unroll
@@ -1119,6 +1144,7 @@ __global__ void __launch_bounds__(NT, 2) k_apply_packed(const pylo_tensor_desc* 
     const float* __restrict__ vp = d.v;
     const float* __restrict__ hap = d.h_a;
     const float* __restrict__ fxp = d.fx;
+    const Peers peers = load_peers(d);
 
     float4 cg, cp, cm0, cm1, cm2, cv;
     auto load_row = [&](int q, float4& g, float4& p, float4& m0, float4& m1, float4& m2, float4& v) {
@@ -1209,8 +1235,10 @@ __global__ void __launch_bounds__(NT, 2) k_apply_packed(const pylo_tensor_desc* 
         float d0, d1, d2, d3, m0, m1, m2, m3;
         unpack2(o0[0], d0, d1); unpack2(o0[1], d2, d3);
         unpack2(o1[0], m0, m1); unpack2(o1[1], m2, m3);
-        st4(op + (int64_t)x * Y + y, make_float4(finish<FAM>(cp.x, d0, m0, fin), finish<FAM>(cp.y, d1, m1, fin),
-                                                 finish<FAM>(cp.z, d2, m2, fin), finish<FAM>(cp.w, d3, m3, fin)));
+        const float4 res = make_float4(finish<FAM>(cp.x, d0, m0, fin), finish<FAM>(cp.y, d1, m1, fin),
+                                       finish<FAM>(cp.z, d2, m2, fin), finish<FAM>(cp.w, d3, m3, fin));
+        st4(op + (int64_t)x * Y + y, res);
+        if (FAM != PYLO_FAM_CELO2) peer_store4(peers, (int64_t)x * Y + y, res);
       }
       if (q + 1 < PK_ROWS) { cg = ng_; cp = np_; cm0 = nm0; cm1 = nm1; cm2 = nm2; cv = nv; }
     }

@@ -96,7 +96,7 @@ class _AdafacFamily(Optimizer):
                 axis = dc - 1 if dc > dr else dc  # AdafacLO_cuda.py:342 (axis 0 is the decay axis)
             tensors.append(LoTensor(
                 p=p.data, m=st["exp_avg"], v=st["exp_avg_sq"], fac_r=st["exp_avg_sq_r"], fac_c=st["exp_avg_sq_c"],
-                fdims=fd, rcm_axis=axis, w=self._w_flat))
+                fdims=fd, rcm_axis=axis, w=self._w_flat, peer_ptrs=getattr(p, "_pylo_peer_ptrs", None)))
         return LoPlan(L.FAM_ADAFAC, tensors, self.device)
 
     def _run_group(self, gi, group, plist, prm, lr, wd, exp_mult, step_mult, clip_norm, stream):

@@ -46,6 +46,7 @@ class LoTensor:
     w: Optional[torch.Tensor] = None    # network weights in family layout
     lr_mult: Optional[torch.Tensor] = None
     slice_last2: bool = False           # normalise features per matrix (last two axes) instead of per tensor
+    peer_ptrs: Optional[Sequence[int]] = None  # device addresses of this parameter in the other ranks' buffers
 
 
 def geometry(shape: Sequence[int], fdims):
@@ -149,6 +150,11 @@ class LoPlan:
             d["out"] = t.out.data_ptr() if t.out is not None else 0
             d["w"] = t.w.data_ptr() if t.w is not None else 0
             d["lr_mult"] = t.lr_mult.data_ptr() if t.lr_mult is not None else 0
+            if t.peer_ptrs:
+                if len(t.peer_ptrs) > L.MAX_PEERS:
+                    raise ValueError(f"at most {L.MAX_PEERS} peers (8 GPUs of one box)")
+                d["p_peer"][: len(t.peer_ptrs)] = list(t.peer_ptrs)
+                d["n_peer"] = len(t.peer_ptrs)
             if t.fdims is None:
                 d["mode"] = L.MODE_VEC1D
                 d["O"] = d["X"] = d["M"] = d["I"] = 1

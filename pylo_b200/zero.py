@@ -159,6 +159,65 @@ class ShardedStep:
         return dist.all_gather_into_tensor(self.flat, self.my_region(), group=self.pg, async_op=async_op)
 
 
+class FusedShardedStep:
+    """Sharded step whose parameter exchange is fused into the apply kernels.
+
+    The flat parameter buffer of every rank is allocated as symmetric memory, so each rank can address
+    its peers' buffers directly.  The kernels that write a parameter store the new value into the
+    owner's buffer and, with plain stores over NVLink, into the same offset of every other rank's
+    buffer (``pylo_tensor_desc.p_peer``); no separate all-gather runs and no SMs are taken away from
+    the apply sweep by a communication kernel.  :meth:`finish` is the only collective left: a
+    one-element all-reduce that orders "all peers have finished writing" before the parameters are
+    read again.  Supported by the AdafacLO / ELO and VeLO kernels (the CELO2 family writes its
+    parameters in a separate tail kernel and keeps the NCCL gather of :class:`StagedShardedStep`).
+    """
+
+    def __init__(self, shapes: Sequence[Tuple[int, ...]], device, init_scale: float = 0.02, seed: int = 1,
+                 process_group=None, cost=None):
+        self.pg = process_group
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+        shapes = [tuple(s) for s in shapes]
+        self.owner = partition(shapes, self.world, cost)
+        self.offsets, self.shard = flat_layout(shapes, self.owner, self.world)
+        n = self.shard * self.world
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm
+
+            self.flat = symm.empty(n, dtype=torch.float32, device=device)
+            self.handle = symm.rendezvous(self.flat, process_group if process_group is not None else dist.group.WORLD)
+            bases = [int(b) for b in self.handle.buffer_ptrs]
+            if bases[self.rank] != self.flat.data_ptr():
+                raise RuntimeError("symmetric memory rendezvous returned an unexpected local address")
+        else:
+            self.flat = torch.zeros(n, dtype=torch.float32, device=device)
+            bases = [self.flat.data_ptr()]
+        gen = torch.Generator(device=device)
+        self.params = []
+        for i, (off, s) in enumerate(zip(self.offsets, shapes)):
+            view = self.flat[off:off + _numel(s)].view(s)
+            gen.manual_seed(seed * 1000003 + i)
+            view.normal_(0.0, init_scale, generator=gen)
+            self.params.append(torch.nn.Parameter(view, requires_grad=True))
+        self.owned = [i for i, r in enumerate(self.owner) if r == self.rank]
+        for i in self.owned:  # where this tensor lives in every other rank's buffer
+            self.params[i]._pylo_peer_ptrs = [bases[r] + 4 * self.offsets[i] for r in range(self.world) if r != self.rank]
+        self._token = torch.zeros(1, dtype=torch.float32, device=device)
+
+    def param_groups(self, is_embedding=None):
+        return [{"params": [self.params[i] for i in self.owned]}]
+
+    def after_group(self, gi: int):
+        return None
+
+    def finish(self):
+        """Order the peers' stores before the next read of the parameters (one tiny all-reduce)."""
+        if self.world > 1:
+            dist.all_reduce(self._token, group=self.pg)
+
+    gather = finish
+
+
 class StagedShardedStep:
     """Sharded step cut into stages whose parameter all-gathers overlap the next stage's kernels.
 

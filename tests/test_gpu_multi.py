@@ -127,6 +127,77 @@ def _staged_worker(rank, world, port, out):
         dist.destroy_process_group()
 
 
+def _fused_worker(rank, world, port, family, out):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from pylo_b200 import models, optim
+        from pylo_b200.zero import FusedShardedStep
+
+        shapes = SHAPES + [(72, 48), (300, 260)]
+        case = dict(CASE, shapes=shapes)
+        shard = FusedShardedStep(shapes, dev, init_scale=0.05, seed=4)
+        start = [p.detach().clone() for p in shard.params]
+        loss = lambda t: torch.tensor(cases.velo_loss(t), device=dev)
+
+        def make(params, sharded):
+            torch.manual_seed(0)
+            if family == "adafaclo":
+                return optim.AdafacLO_CUDA(params, lr=1e-2, network=models.MetaMLP(39, 32, 1))
+            rnn, mlp = models.VeLORNN(lstm_hidden_size=32), models.VeLOMLP()
+            with torch.no_grad():
+                for name, p in mlp.named_parameters():
+                    if name.endswith("_") or "_." in name:
+                        p.mul_(0.05)
+            kw = dict(all_shapes=shapes, owned=shard.owned) if sharded else {}
+            return optim.VeLO_CUDA(params, lr=10.0, num_steps=100, rnn=rnn, mlp=mlp, **kw)
+
+        opt = make([shard.params[i] for i in shard.owned], True)
+        for t in (1, 2, 3):
+            grads = cases.grads_at(case, t)
+            for i in shard.owned:
+                shard.params[i].grad = grads[i].to(dev)
+            opt.step(loss(t)) if family == "velo" else opt.step()
+            shard.finish()
+        torch.cuda.synchronize()
+        ref = [torch.nn.Parameter(v.clone()) for v in start]
+        opt1 = make(ref, False)
+        for t in (1, 2, 3):
+            for p, g in zip(ref, cases.grads_at(case, t)):
+                p.grad = g.to(dev)
+            opt1.step(loss(t)) if family == "velo" else opt1.step()
+        torch.cuda.synchronize()
+        same = all(torch.equal(a.detach(), b.detach()) for a, b in zip(shard.params, ref))
+        moved = any(not torch.equal(a.detach(), b) for a, b in zip(ref, start))
+        out.put((rank, "ok" if same and moved else f"same={same} moved={moved}"))
+    except Exception:  # pragma: no cover
+        import traceback
+
+        out.put((rank, traceback.format_exc()[-800:]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("family", ["adafaclo", "velo"])
+def test_two_rank_fused_exchange_is_bit_identical(family):
+    """Parameters reach the other rank as peer stores from the apply kernels (no all-gather)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_fused_worker, args=(r, 2, port, family, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results
+
+
 def test_two_rank_staged_step_with_overlapped_gathers_is_bit_identical():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
