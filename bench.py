@@ -102,10 +102,15 @@ def build_optimizer(args, shard, params):
         rnn, mlp = seeded_networks(k)
         return optim.VeLO_CUDA(params, lr=1e-3, num_steps=10000, rnn=rnn, mlp=mlp, process_group=shard.pg,
                                all_shapes=[tuple(p.shape) for p in shard.params], owned=shard.owned)
+    from pylo_b200.zero import FusedShardedStep
+
+    # several param groups even on one GPU: the optimizer runs them in order, so the end-to-end leg can
+    # let group k compute while the gradients of group k+1 are still arriving from the host
+    groups = shard.param_groups(groups=args.blocks) if isinstance(shard, FusedShardedStep) else shard.param_groups()
     if k == "adafaclo":
-        opt = optim.AdafacLO_CUDA(shard.param_groups(), lr=1e-3, step_mult=0.01, exp_mult=0.001, network=seeded_networks(k))
+        opt = optim.AdafacLO_CUDA(groups, lr=1e-3, step_mult=0.01, exp_mult=0.001, network=seeded_networks(k))
     elif k == "elo":
-        opt = optim.ELO_CUDA(shard.param_groups(), lr=1e-3, weight_decay=0.1, clip_grad=True, network=seeded_networks(k))
+        opt = optim.ELO_CUDA(groups, lr=1e-3, weight_decay=0.1, clip_grad=True, network=seeded_networks(k))
     else:
         cls = optim.CELO2_CUDA if k == "celo2" else optim.ELO_CELO2_CUDA
         opt = cls(shard.param_groups(is_embedding_shape), lr=1e-3, weight_decay=0.1,
@@ -269,7 +274,8 @@ def run_b200(args):
         exchange = "fused" if args.optimizer in ("adafaclo", "elo", "velo") else "staged"
     if world == 1:
         exchange = "none"
-    if exchange == "fused":    # parameters reach the other ranks as peer stores from the apply kernels
+    if exchange == "fused" or (world == 1 and args.optimizer in ("adafaclo", "elo")):
+        # N>1: parameters reach the other ranks as peer stores from the apply kernels; N=1: plain flat buffer
         shard = FusedShardedStep(shapes, dev, init_scale=0.02, seed=1)
     elif args.optimizer == "velo":  # its LSTM needs every tensor's statistics before any tensor is applied
         shard = ShardedStep.from_shapes(shapes, dev, init_scale=0.02, seed=1)
@@ -354,12 +360,25 @@ def run_b200(args):
         h2d = sum(p.numel() for p in params) * 4
         d2h = len(owned) * 4
 
+        copy_stream = torch.cuda.Stream(device=dev)
+        group_params = [list(g["params"]) for g in opt.param_groups] if not velo else [params]
+        events = [torch.cuda.Event() for _ in group_params]
+
         def e2e_step():
-            for p in params:
-                p.grad.copy_(pinned[tuple(p.shape)], non_blocking=True)
+            # gradients of group k+1 arrive from pinned host memory while group k computes
+            copy_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(copy_stream):
+                for gi, plist in enumerate(group_params):
+                    for p in plist:
+                        p.grad.copy_(pinned[tuple(p.shape)], non_blocking=True)
+                    events[gi].record(copy_stream)
+            if velo:
+                torch.cuda.current_stream().wait_event(events[0])
             one_step()
             return shard.flat.index_select(0, probe_idx).cpu()
 
+        if not velo:
+            opt.before_group = lambda gi: torch.cuda.current_stream().wait_event(events[gi])
         e2e_step()
         barrier()
         ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]

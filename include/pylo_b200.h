@@ -131,7 +131,7 @@ typedef struct pylo_step_params {
   int32_t family;
   int32_t nan_to_num;     /* ELO: torch.nan_to_num on the (scaled) gradient */
   int32_t wd_mode;        /* 0 none in kernel; 1 AdafacLO (after update, on new p); 2 ELO (on old p); 3 VeLO (lr_eff) */
-  int32_t reserved;
+  float step_delta;       /* added to every desc.step: lets the host advance the step count without re-uploading the table */
   float w_m[3];           /* 1 - beta_m[k], computed in fp32 as the reference does */
   float w_v;              /* 1 - beta_rms */
   float w_f[3];           /* 1 - beta_fac[k] */

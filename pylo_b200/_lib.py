@@ -52,7 +52,7 @@ ADAM_DTYPE = np.dtype(
 
 class StepParams(C.Structure):
     _fields_ = [
-        ("family", C.c_int32), ("nan_to_num", C.c_int32), ("wd_mode", C.c_int32), ("reserved", C.c_int32),
+        ("family", C.c_int32), ("nan_to_num", C.c_int32), ("wd_mode", C.c_int32), ("step_delta", C.c_float),
         ("w_m", C.c_float * 3), ("w_v", C.c_float), ("w_f", C.c_float * 3),
         ("eps_v", C.c_float), ("eps_feat", C.c_float), ("eps_norm", C.c_float), ("clip_val", C.c_float),
         ("gnorm_sq", C.c_void_p),

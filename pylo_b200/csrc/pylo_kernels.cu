@@ -536,7 +536,7 @@ __global__ void __launch_bounds__(NT) k_prep_apply(const pylo_tensor_desc* __res
     if (FAM == PYLO_FAM_ADAFAC) {
       const float tau[11] = {1.f, 3.f, 10.f, 30.f, 100.f, 300.f, 1000.f, 3000.f, 10000.f, 30000.f, 100000.f};
 #pragma unroll
-      for (int t = 0; t < 11; ++t) b = fmaf(w1_at(FAM, w, tid, 28 + t), tanhf(d.step / tau[t] - 1.0f), b);
+      for (int t = 0; t < 11; ++t) b = fmaf(w1_at(FAM, w, tid, 28 + t), tanhf((d.step + prm.step_delta) / tau[t] - 1.0f), b);
     }
     s_b1[tid] = b;
   }

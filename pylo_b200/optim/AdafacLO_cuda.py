@@ -53,6 +53,7 @@ class _AdafacFamily(Optimizer):
         self.process_group = None   # set (or set _sharded) when the tensors of the model are split over ranks
         self._sharded = False
         self.after_group = None     # optional callable(group index), called once a param group's kernels are enqueued
+        self.before_group = None    # optional callable(group index), called before a param group's first kernel
         # fp32 values of 1 - beta, read back once (the reference evaluates them on the device every step)
         self._w_m, self._w_f = one_minus(self.beta_m), one_minus(self.beta_adafactor)
         self._w_v = one_minus(self.beta_rms)[0]
@@ -117,6 +118,8 @@ class _AdafacFamily(Optimizer):
         plan.set_field("step_mult", step_mult)
         plan.set_field("clip_norm", clip_norm)
         plan.refresh([p.grad for p in plist], steps=steps)
+        if self.before_group is not None:
+            self.before_group(gi)
         plan.run_front(prm, stream)
         plan.run_back(prm, stream)
         if self.after_group is not None:

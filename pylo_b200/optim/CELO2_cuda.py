@@ -75,6 +75,7 @@ class _Celo2Family(Optimizer):
         self.process_group = None   # set (or set _sharded) when the tensors of the model are split over ranks
         self._sharded = False
         self.after_group = None     # optional callable(group index), called once a param group's kernels are enqueued
+        self.before_group = None    # optional callable(group index), called before a param group's first kernel
         # fp32 values of 1 - beta, read back once (the reference evaluates them on the device every step)
         self._w_m, self._w_f = one_minus(self.beta_m), one_minus(self.beta_fac)
         self._w_v = float(1 - self.beta_rms[-1])
@@ -195,6 +196,8 @@ class _Celo2Family(Optimizer):
                 cached = (sig, self._build_group_plan(gi, group, plist))
                 self._plans[gi] = cached
             plan = cached[1]
+            if self.before_group is not None:
+                self.before_group(gi)
             prm = self._params_struct(group, gnorm_ptr)
             clip_norm = float(group["clip_norm"]) if group["clip_grad"] else 0.0
             lr = float(group["lr"])

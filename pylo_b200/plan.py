@@ -299,8 +299,15 @@ class LoPlan:
                 self._keepalive.append(g)
             ptrs[i] = g.data_ptr()
         self.tdesc.host["g"][:] = ptrs
+        self.step_delta = 0.0
         if steps is not None:
-            self.set_field("step", steps)
+            # when every tensor advanced by the same amount since the table was last written, leave the
+            # table alone and hand the kernels the difference (no upload on the step path)
+            delta = np.asarray(steps, dtype=np.float64) - self.tdesc.host["step"].astype(np.float64)
+            if len(delta) and np.all(delta == delta[0]) and 0 <= delta[0] < 2**20 and self.tdesc._last is not None:
+                self.step_delta = float(delta[0])
+            else:
+                self.set_field("step", steps)
         self.tdesc.upload()
         if self.sliced:
             self.desc.host["g"][:] = [ptrs[i] + np.uint64(4 * off) for i, off in self.unit_owner]
@@ -332,6 +339,7 @@ class LoPlan:
 
     def run_front(self, prm: L.StepParams, stream: int, reverse_b: bool = True):
         """Phases A, A2, B, B2."""
+        prm.step_delta = getattr(self, "step_delta", 0.0)
         pp = C.byref(prm)
         if self.n_atiles or self.n_generic:
             self._call("rowcol_sums", L.lib.pylo_b200_rowcol_sums, self.tdesc.ptr, self.atiles.ptr, self.n_atiles,

@@ -159,6 +159,21 @@ class ShardedStep:
         return dist.all_gather_into_tensor(self.flat, self.my_region(), group=self.pg, async_op=async_op)
 
 
+def split_in_groups(params, groups: int):
+    """Consecutive runs of ``params`` with similar numbers of elements, as optimizer param groups."""
+    total = sum(p.numel() for p in params)
+    out, cur, acc = [], [], 0
+    for p in params:
+        cur.append(p)
+        acc += p.numel()
+        if len(out) < groups - 1 and acc >= total * (len(out) + 1) / groups:
+            out.append({"params": cur})
+            cur = []
+    if cur:
+        out.append({"params": cur})
+    return out
+
+
 class FusedShardedStep:
     """Sharded step whose parameter exchange is fused into the apply kernels.
 
@@ -204,8 +219,10 @@ class FusedShardedStep:
             self.params[i]._pylo_peer_ptrs = [bases[r] + 4 * self.offsets[i] for r in range(self.world) if r != self.rank]
         self._token = torch.zeros(1, dtype=torch.float32, device=device)
 
-    def param_groups(self, is_embedding=None):
-        return [{"params": [self.params[i] for i in self.owned]}]
+    def param_groups(self, is_embedding=None, groups: int = 1):
+        """The owned tensors as ``groups`` param groups of similar size, in buffer order (the optimizer
+        runs its param groups one after the other, which lets a caller pipeline gradient arrival)."""
+        return split_in_groups([self.params[i] for i in self.owned], groups)
 
     def after_group(self, gi: int):
         return None
