@@ -50,7 +50,7 @@ def parse():
     ap.add_argument("--optimizer", default="adafaclo", choices=sorted(STEP_BYTES))
     ap.add_argument("--layers", type=int, default=None, help="llama3_8b only: number of transformer layers (default 32)")
     ap.add_argument("--no-orthogonalize", action="store_true", help="celo2 family: skip Newton-Schulz")
-    ap.add_argument("--blocks", type=int, default=4, help="N>1: stages whose parameter all-gathers overlap the next stage")
+    ap.add_argument("--blocks", type=int, default=8, help="N>1: stages whose parameter all-gathers overlap the next stage")
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "staged"],
                     help="N>1: how updated parameters reach the other ranks (peer stores fused into the apply kernels, "
                          "or NCCL all-gathers per block)")
