@@ -37,7 +37,7 @@ APPLY_BYTES = 28
 B_BYTES = 40  # state_moments sweep: reads g, p, m(3), v; writes m(3), v
 # DRAM bytes per element (dram__bytes_read.sum + dram__bytes_write.sum) of each dominant kernel, from ncu
 # captures of a 4096 x 4096 case (profiles/*.md); traffic grows in proportion to the elements processed
-NCU_TRAFFIC_PER_ELEM = {("adafaclo", "apply_cols"): 27.45, ("elo", "apply_cols"): 27.45}
+NCU_TRAFFIC_PER_ELEM = {("adafaclo", "apply_cols"): 27.58, ("elo", "apply_cols"): 27.58}
 
 
 def parse():
