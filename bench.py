@@ -50,6 +50,8 @@ def parse():
     ap.add_argument("--optimizer", default="adafaclo", choices=sorted(STEP_BYTES))
     ap.add_argument("--layers", type=int, default=None, help="llama3_8b only: number of transformer layers (default 32)")
     ap.add_argument("--no-orthogonalize", action="store_true", help="celo2 family: skip Newton-Schulz")
+    ap.add_argument("--ns-precision", default="fp32", choices=["fp32", "3xtf32"],
+                    help="celo2 family: Newton-Schulz products in fp32 (reference arithmetic) or as three TF32 tensor-core GEMMs")
     ap.add_argument("--blocks", type=int, default=8, help="N>1: stages whose parameter all-gathers overlap the next stage")
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "staged"],
                     help="N>1: how updated parameters reach the other ranks (peer stores fused into the apply kernels, "
@@ -114,7 +116,7 @@ def build_optimizer(args, shard, params):
     else:
         cls = optim.CELO2_CUDA if k == "celo2" else optim.ELO_CELO2_CUDA
         opt = cls(shard.param_groups(is_embedding_shape), lr=1e-3, weight_decay=0.1,
-                  orthogonalize=not args.no_orthogonalize, network=seeded_networks(k))
+                  orthogonalize=not args.no_orthogonalize, network=seeded_networks(k), ns_precision=args.ns_precision)
     opt._sharded, opt.process_group = shard.world > 1, shard.pg
     opt.after_group = shard.after_group
     return opt

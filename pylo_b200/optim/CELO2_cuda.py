@@ -29,7 +29,7 @@ from torch.optim import Optimizer
 from .. import _lib as L
 from ..models.CELO2_MLP import CELO2MLP
 from ..plan import GradNorm, LoPlan, LoTensor, current_stream_ptr, one_minus
-from ._common import ItemPlan, factored_dims_argsort, newton_schulz, require_cuda_param
+from ._common import ItemPlan, factored_dims_argsort, newton_schulz, newton_schulz_3xtf32, require_cuda_param
 
 _IN, _HID = 30, 8
 
@@ -72,6 +72,7 @@ class _Celo2Family(Optimizer):
         self._w_flat = torch.cat([t.reshape(-1) for t in (self.w_in, self.b_in, self.w_h, self.b_h, self.w_out, self.b_out)]).contiguous()
         self._plans = {}
         self._gnorm = None
+        self.ns_precision = "fp32"  # "3xtf32": Newton-Schulz products as three TF32 tensor-core GEMMs (not bit-identical)
         self.process_group = None   # set (or set _sharded) when the tensors of the model are split over ranks
         self._sharded = False
         self.after_group = None     # optional callable(group index), called once a param group's kernels are enqueued
@@ -216,7 +217,8 @@ class _Celo2Family(Optimizer):
                 for ti, (p, t) in enumerate(zip(plan["lo_params"], lo.tensors)):
                     step = t.out
                     if group["orthogonalize"] and step.dim() >= 2:
-                        step = newton_schulz(step, self.ns_coeffs, self.ns_iters, self.ns_eps).contiguous()
+                        ns = newton_schulz_3xtf32 if self.ns_precision == "3xtf32" else newton_schulz
+                        step = ns(step, self.ns_coeffs, self.ns_iters, self.ns_eps).contiguous()
                     keep.append(step)
                 it = post.items
                 base_s = np.fromiter((k.data_ptr() for k in keep), dtype=np.uint64, count=len(keep))
@@ -277,7 +279,7 @@ class CELO2_CUDA(_Celo2Family):
                  initial_rms_decays=(0.95,), initial_adafactor_decays=(0.9, 0.99, 0.999), exp_mult=0.0, rmsmult=1.0,
                  param_scale_mult=False, ns_coeffs=(3.4445, -4.7750, 2.0315), ns_iters=5, ns_eps=1e-8,
                  grad_clip_val=1000.0, hf_key: Optional[str] = "DiamondXL/celo2",
-                 checkpoint_path: Optional[str] = None, network: Optional[CELO2MLP] = None):
+                 checkpoint_path: Optional[str] = None, network: Optional[CELO2MLP] = None, ns_precision: str = "fp32"):
         defaults = dict(
             lr=lr, weight_decay=weight_decay, adam_lr_mult=adam_lr_mult,
             adam_weight_decay=(adam_weight_decay if adam_weight_decay is not None else weight_decay),
@@ -288,6 +290,9 @@ class CELO2_CUDA(_Celo2Family):
         self.adam_eps = adam_eps
         self._setup(params, defaults, initial_momentum_decays, initial_rms_decays, initial_adafactor_decays,
                     ns_coeffs, ns_iters, ns_eps, ff_hidden_size, ff_hidden_layers, hf_key, checkpoint_path, network)
+        if ns_precision not in ("fp32", "3xtf32"):
+            raise ValueError("ns_precision must be 'fp32' or '3xtf32'")
+        self.ns_precision = ns_precision
 
 
 class ELO_CELO2_CUDA(_Celo2Family):
@@ -302,7 +307,7 @@ class ELO_CELO2_CUDA(_Celo2Family):
                  initial_adafactor_decays=(0.9, 0.99, 0.999), exp_mult=0.0, rmsmult=1.0, param_scale_mult=False,
                  ns_coeffs=(3.4445, -4.7750, 2.0315), ns_iters=5, ns_eps=1e-8, grad_clip_val=1000.0,
                  hf_key: Optional[str] = "DiamondXL/elo-celo2", checkpoint_path: Optional[str] = None,
-                 network: Optional[CELO2MLP] = None):
+                 network: Optional[CELO2MLP] = None, ns_precision: str = "fp32"):
         defaults = dict(
             lr=lr, weight_decay=weight_decay, adam_lr_mult=adam_lr_mult,
             adam_weight_decay=(adam_weight_decay if adam_weight_decay is not None else weight_decay),
@@ -311,3 +316,6 @@ class ELO_CELO2_CUDA(_Celo2Family):
             is_embedding=False)
         self._setup(params, defaults, initial_momentum_decays, initial_rms_decays, initial_adafactor_decays,
                     ns_coeffs, ns_iters, ns_eps, ff_hidden_size, ff_hidden_layers, hf_key, checkpoint_path, network)
+        if ns_precision not in ("fp32", "3xtf32"):
+            raise ValueError("ns_precision must be 'fp32' or '3xtf32'")
+        self.ns_precision = ns_precision
