@@ -128,16 +128,27 @@ class _Celo2Family(Optimizer):
             (adam if to_adam else lo).append(p)
         plan = {"lo_params": lo, "adam_params": adam, "lo": None, "adam": None, "post": None}
         if lo:
+            # raw-step buffers of equally shaped tensors are slices of one stacked tensor, so that
+            # Newton-Schulz runs once per shape as a batched product instead of once per tensor
+            by_shape = {}
+            for ti, p in enumerate(lo):
+                by_shape.setdefault(tuple(p.shape), []).append(ti)
+            stacks, out_of = [], {}
+            for shape, members in by_shape.items():
+                stacked = torch.empty((len(members),) + shape, dtype=torch.float32, device=self.device)
+                stacks.append((stacked, members))
+                for j, ti in enumerate(members):
+                    out_of[ti] = stacked[j]
+            plan["stacks"] = stacks
             tensors = []
-            for p in lo:
+            for ti, p in enumerate(lo):
                 st = self.state[p]
                 fd = factored_dims_argsort(tuple(p.shape))
                 if fd is None:
                     raise ValueError(f"{self._name}: tensors with fewer than 2 dims need use_adamw_for_1d=True")
-                st_out = torch.empty_like(p)
                 tensors.append(LoTensor(
                     p=p.data, m=st["mom"], v=st["rms"], fac_r=st["fac_r"], fac_c=st["fac_c"], fdims=fd,
-                    rcm_axis=fd[0] + 1, out=st_out, w=self._w_flat, slice_last2=True))
+                    rcm_axis=fd[0] + 1, out=out_of[ti], w=self._w_flat, slice_last2=True))
             plan["lo"] = LoPlan(L.FAM_CELO2, tensors, self.device)
             # the tail works on matrices: the last two axes of every tensor
             post_sizes, post_owner = [], []
@@ -213,13 +224,16 @@ class _Celo2Family(Optimizer):
                 lo.run_front(prm, stream)
                 lo.run_back(prm, stream)
                 post = plan["post"]
-                keep = []
-                for ti, (p, t) in enumerate(zip(plan["lo_params"], lo.tensors)):
-                    step = t.out
-                    if group["orthogonalize"] and step.dim() >= 2:
-                        ns = newton_schulz_3xtf32 if self.ns_precision == "3xtf32" else newton_schulz
-                        step = ns(step, self.ns_coeffs, self.ns_iters, self.ns_eps).contiguous()
-                    keep.append(step)
+                keep = [t.out for t in lo.tensors]
+                if group["orthogonalize"]:
+                    ns = newton_schulz_3xtf32 if self.ns_precision == "3xtf32" else newton_schulz
+                    for stacked, members in plan["stacks"]:
+                        # batches of at most ~64 M elements keep the iteration's temporaries small
+                        per = max(1, (64 << 20) // max(1, stacked[0].numel()))
+                        for c0 in range(0, len(members), per):
+                            res = ns(stacked[c0:c0 + per], self.ns_coeffs, self.ns_iters, self.ns_eps).contiguous()
+                            for j, ti in enumerate(members[c0:c0 + per]):
+                                keep[ti] = res[j]
                 it = post.items
                 base_s = np.fromiter((k.data_ptr() for k in keep), dtype=np.uint64, count=len(keep))
                 base_p = np.fromiter((p.data_ptr() for p in plan["lo_params"]), dtype=np.uint64, count=len(keep))
