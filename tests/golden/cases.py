@@ -77,7 +77,7 @@ CELO2_CASES = [
 _MLP_SHAPES = [(128, 784), (128,), (128, 128), (128,), (10, 128), (10,)]
 
 ADAFAC_CASES = [
-    # the CPU-runnable BASELINE configuration: 784-128-128-10 MLP, 10 steps, lr 1e-3
+    # the CPU-runnable benchmark configuration: 784-128-128-10 MLP, 10 steps, lr 1e-3
     dict(name="adafaclo_mlp", family="adafaclo", shapes=_MLP_SHAPES, net_seed=0, init_seed=1, init_scale=0.05,
          grad_seed=2, grad_scale=1e-3, steps=10, record=[1, 10], sample_stride=29,
          hparams=dict(lr=1e-3, step_mult=0.01, exp_mult=0.001)),

@@ -1,7 +1,7 @@
 """Generate the golden trajectories under tests/golden/ from the reference's own code.
 
-Run once, in a container that holds the reference checkout (default
-``/root/reference``; override with ``PYLO_REFERENCE``):
+Run once, where a checkout of the reference is available; point ``PYLO_REFERENCE`` at it
+(default: a sibling directory ``reference`` next to this repository):
 
     python tests/golden/make_golden.py
 
@@ -36,7 +36,8 @@ import cases  # noqa: E402
 
 
 def load_reference():
-    ref = os.environ.get("PYLO_REFERENCE", "/root/reference")
+    default = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")
+    ref = os.environ.get("PYLO_REFERENCE", default)
     mup = types.ModuleType("mup")
     mup_optim = types.ModuleType("mup.optim")
     mup_optim.process_param_groups = lambda *a, **k: None

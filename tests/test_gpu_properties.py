@@ -1,6 +1,6 @@
 """GPU checks beyond the golden trajectories: resume format, ragged shapes, full-size properties.
 
-At the full BASELINE size (4096 x 4096) the oracle would take minutes per family, so the checks there
+At the full benchmark size (4096 x 4096) the oracle would take minutes per family, so the checks there
 are size-independent properties: two different code paths of the library (the float4 path and the
 scalar generic path, selected by the alignment of the tensors) must agree, and repeated runs must be
 bit-identical.
@@ -159,7 +159,7 @@ def test_state_keys_and_shapes_are_the_reference_format():
 
 @pytest.mark.parametrize("family", ["adafaclo", "celo2", "velo"])
 def test_full_size_float4_and_generic_paths_agree(family):
-    """4096 x 4096 (the BASELINE single-tensor size): the same values once 16-byte aligned (float4 path)
+    """4096 x 4096 (the single-tensor benchmark size): the same values once 16-byte aligned (float4 path)
     and once shifted by one float (scalar generic path) must give the same update."""
     n = 4096
     gen = torch.Generator(device="cuda").manual_seed(3)
