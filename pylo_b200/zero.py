@@ -336,3 +336,42 @@ def sharded_optimizer(cls, shard: ShardedStep, **kwargs):
         opt._sharded = shard.world > 1
         opt.process_group = shard.pg
     return opt
+
+
+def consolidate_state_dict(optimizer, shard, dst: int = 0):
+    """The single-process ``state_dict`` of a sharded run, rebuilt on rank ``dst`` (``None`` elsewhere).
+
+    Every rank's optimizer holds the state of the tensors it owns.  This gathers them (as CPU tensors)
+    and re-keys them by the tensor's position in the global parameter order, which is exactly what an
+    optimizer built over *all* parameters in one process would save, so the result loads into such an
+    optimizer (or into the reference's classes).  Param-group hyper-parameters are taken from this
+    rank's first group.  VeLO's extra entries (``loss_buffer``, ``lstm_hidden_state``, ``num_steps``) are
+    replicated on every rank and are copied from rank ``dst``.
+    """
+    local = optimizer.state_dict()
+    order = [i for g in optimizer.param_groups for i in _global_indices(g["params"], shard)]
+    to_cpu = lambda v: v.detach().cpu() if torch.is_tensor(v) else v
+    mine = {order[k]: {name: to_cpu(v) for name, v in st.items()} for k, st in local["state"].items()}
+    world = shard.world
+    gathered = [None] * world if (shard.rank == dst or world == 1) else None
+    if world > 1:
+        dist.gather_object(mine, gathered, dst=dst, group=shard.pg)
+    else:
+        gathered = [mine]
+    if shard.rank != dst:
+        return None
+    state = {}
+    for part in gathered:
+        state.update(part)
+    group = {k: v for k, v in local["param_groups"][0].items() if k != "params"}
+    group["params"] = list(range(len(shard.params)))
+    out = {"state": {i: state[i] for i in sorted(state)}, "param_groups": [group]}
+    for extra in ("loss_buffer", "lstm_hidden_state", "num_steps"):
+        if extra in local:
+            out[extra] = local[extra]
+    return out
+
+
+def _global_indices(params, shard):
+    pos = {id(p): i for i, p in enumerate(shard.params)}
+    return [pos[id(p)] for p in params]

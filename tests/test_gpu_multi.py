@@ -172,6 +172,19 @@ def _fused_worker(rank, world, port, family, out):
         torch.cuda.synchronize()
         same = all(torch.equal(a.detach(), b.detach()) for a, b in zip(shard.params, ref))
         moved = any(not torch.equal(a.detach(), b) for a, b in zip(ref, start))
+        # the consolidated checkpoint equals what the single-process optimizer saves
+        from pylo_b200.zero import consolidate_state_dict
+
+        full = consolidate_state_dict(opt, shard, dst=0)
+        if rank == 0:
+            want = opt1.state_dict()["state"]
+            for i, st in want.items():
+                for name, v in st.items():
+                    got = full["state"][i][name]
+                    if torch.is_tensor(v):
+                        same = same and torch.equal(got, v.detach().cpu())
+                    else:
+                        same = same and got == v
         out.put((rank, "ok" if same and moved else f"same={same} moved={moved}"))
     except Exception:  # pragma: no cover
         import traceback
