@@ -276,13 +276,29 @@ def run_b200(args):
         exchange = "fused" if args.optimizer in ("adafaclo", "elo", "velo") else "staged"
     if world == 1:
         exchange = "none"
+    shard = None
     if exchange == "fused" or (world == 1 and args.optimizer in ("adafaclo", "elo")):
         # N>1: parameters reach the other ranks as peer stores from the apply kernels; N=1: plain flat buffer
-        shard = FusedShardedStep(shapes, dev, init_scale=0.02, seed=1)
+        ok, why = 1, ""
+        try:
+            shard = FusedShardedStep(shapes, dev, init_scale=0.02, seed=1)
+        except Exception as e:  # symmetric memory unavailable on this box: fall back to NCCL gathers
+            ok, why = 0, repr(e)
+        if world > 1:
+            flag = torch.tensor([ok], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            ok = int(flag.item())
+        if not ok:
+            if rank == 0:
+                print(f"fused exchange unavailable ({why or 'another rank failed'}); using NCCL gathers", file=sys.stderr)
+            shard, exchange = None, "staged"
+            torch.cuda.empty_cache()
+    if shard is not None:
+        pass
     elif args.optimizer == "velo":  # its LSTM needs every tensor's statistics before any tensor is applied
         shard = ShardedStep.from_shapes(shapes, dev, init_scale=0.02, seed=1)
     else:                      # NCCL all-gathers per block, overlapped with the next block's kernels
-        shard = StagedShardedStep(shapes, dev, blocks=args.blocks, init_scale=0.02, seed=1)
+        shard = StagedShardedStep(shapes, dev, blocks=min(args.blocks, 4), init_scale=0.02, seed=1)
     args.exchange_used = exchange
     owned = shard.owned
     params = [shard.params[i] for i in owned]
