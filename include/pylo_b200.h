@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define PYLO_B200_ABI_VERSION 5
+#define PYLO_B200_ABI_VERSION 6
 
 /* optimizer families (which feature set / network geometry a launch uses) */
 #define PYLO_FAM_ADAFAC 0 /* AdafacLO_CUDA, ELO_CUDA: 28+11 features, 39-32-32-2 */
@@ -139,6 +139,8 @@ typedef struct pylo_step_params {
   float eps_feat;         /* inside rsqrt(v + eps): 1e-6 AdafacLO/ELO/VeLO, 1e-8 CELO2 */
   float eps_norm;         /* inside rsqrt(S/n + eps): 1e-5 AdafacLO/ELO/VeLO, 1e-9 CELO2 */
   float clip_val;         /* element-wise clamp of the gradient; +inf for none */
+  int32_t no_tables;      /* prep_apply: skip the per-row / per-column first-layer tables (the tensor-core apply
+                             kernel builds its operands from the factor vectors itself) */
   const float* gnorm_sq;  /* device scalar: sum of squares of all gradients, or NULL */
 } pylo_step_params;
 
@@ -229,6 +231,17 @@ int pylo_b200_apply(const pylo_tensor_desc* descs, const pylo_tile* tiles, int n
  * With one of the FAST2D kernels in use pylo_b200_apply handles the GENERIC and VEC1D units only. */
 int pylo_b200_apply_adafac_cols(const pylo_tensor_desc* descs, const pylo_atile* ctiles, int n_ctiles,
                                 const pylo_step_params* prm, void* stream);
+
+/* Phase C for the FAST2D tensors of the ADAFAC family on the tensor cores (no reference counterpart: the
+ * reference evaluates the network with scalar FMAs, lo_kernel_apply learned_optimizer.cu:236-284).  Same inputs
+ * and outputs as pylo_b200_apply_adafac_cols; the two hidden layers run as tcgen05 TF32 products with every
+ * operand split into a high and a low TF32 part (three products per layer), which keeps a 32-term dot product
+ * within ~3e-7 of the sum of its terms' magnitudes; non-finite features give NaN where the scalar path may give
+ * an infinity.  ttiles: strip = row-strip index, cb = block of 128 columns, pad_ = rows per work item (a multiple
+ * of 4).  status: device int the kernel ORs 1 into if a wait on the tensor core ran out (results are then
+ * invalid); may be NULL. */
+int pylo_b200_apply_adafac_tc(const pylo_tensor_desc* descs, const pylo_atile* ttiles, int n_ttiles,
+                              const pylo_step_params* prm, int* status, void* stream);
 
 /* Phase C for the FAST2D tensors of the CELO2 and VELO families (same arithmetic as pylo_b200_apply, done on
  * pairs of adjacent elements with packed fp32x2 instructions).  ctiles: strip = row-tile index, cb = column-tile

@@ -16,7 +16,7 @@ SUMS_STRIDE = 48
 TILE_ELEMS = 16384
 A_COLS = 1024
 WFOLD_STRIDE = 2432
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 FAM_ADAFAC, FAM_CELO2, FAM_VELO = 0, 1, 2
 MODE_FAST2D, MODE_GENERIC, MODE_VEC1D = 0, 1, 2
@@ -55,7 +55,7 @@ class StepParams(C.Structure):
         ("family", C.c_int32), ("nan_to_num", C.c_int32), ("wd_mode", C.c_int32), ("step_delta", C.c_float),
         ("w_m", C.c_float * 3), ("w_v", C.c_float), ("w_f", C.c_float * 3),
         ("eps_v", C.c_float), ("eps_feat", C.c_float), ("eps_norm", C.c_float), ("clip_val", C.c_float),
-        ("gnorm_sq", C.c_void_p),
+        ("no_tables", C.c_int32), ("gnorm_sq", C.c_void_p),
     ]
 
 
@@ -94,6 +94,7 @@ def _load():
         "pylo_b200_prep_apply": [vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_apply": [vp, vp, i32, i32, C.POINTER(StepParams), vp],
         "pylo_b200_apply_adafac_cols": [vp, vp, i32, C.POINTER(StepParams), vp],
+        "pylo_b200_apply_adafac_tc": [vp, vp, i32, C.POINTER(StepParams), vp, vp],
         "pylo_b200_apply_packed": [vp, vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_celo2_post_sums": [vp, vp, i32, vp],
         "pylo_b200_celo2_post_apply": [vp, vp, i32, vp],

@@ -565,7 +565,7 @@ __global__ void __launch_bounds__(NT) k_prep_apply(const pylo_tensor_desc* __res
       o[L::SC + 1] = d.lr_mult ? d.lr * d.lr_mult[0] : d.lr;
     }
   }
-  if (d.mode != PYLO_MODE_FAST2D) return;
+  if (d.mode != PYLO_MODE_FAST2D || prm.no_tables) return;
   // first-layer contribution of the features that depend only on the "a" index (plus bias) / "b" index
   const int64_t La = d.X, Lb = d.Y;
   const int ka = d.r_is_a ? F::R : F::C, kra = d.r_is_a ? F::RR : F::RC;
@@ -1033,6 +1033,8 @@ __global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const 
     }  // sub-tiles
   }
 }
+
+#include "pylo_apply_tc.cuh"
 
 // ================================================================================================
 // Phase C for CELO2 / ELO_CELO2 / VeLO on FAST2D tensors: packed kernel.
@@ -1726,6 +1728,22 @@ int pylo_b200_apply_adafac_cols(const pylo_tensor_desc* descs, const pylo_atile*
     configured = true;
   }
   k_apply_adafac_cols<<<grid_for(n_ctiles, CC_CTAS_PER_SM), NT, sizeof(CcSmem), (cudaStream_t)stream>>>(descs, ctiles, n_ctiles, *prm);
+  return launch_status();
+}
+
+int pylo_b200_apply_adafac_tc(const pylo_tensor_desc* descs, const pylo_atile* ttiles, int n_ttiles,
+                              const pylo_step_params* prm, int* status, void* stream) {
+  CHECK_ARG(descs && ttiles && prm && n_ttiles >= 0 && prm->family == PYLO_FAM_ADAFAC);
+  if (n_ttiles == 0) return 0;
+  // more than half an SM's shared memory: one CTA per SM, which then owns all of the SM's tensor memory
+  constexpr int smem = sizeof(TcSmem) > 120 * 1024 ? (int)sizeof(TcSmem) : 120 * 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(k_apply_adafac_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  k_apply_adafac_tc<<<grid_for(n_ttiles, 1), TC_NT, smem, (cudaStream_t)stream>>>(descs, ttiles, n_ttiles, *prm, status);
   return launch_status();
 }
 

@@ -50,6 +50,8 @@ class _AdafacFamily(Optimizer):
         self._w_flat = torch.cat([t.reshape(-1) for t in flat]).to(self.device).contiguous()
         self._plans = {}
         self._gnorm = None
+        if self.mlp_precision not in ("fp32", "3xtf32"):
+            raise ValueError(f"mlp_precision must be 'fp32' or '3xtf32', got {self.mlp_precision!r}")
         self.process_group = None   # set (or set _sharded) when the tensors of the model are split over ranks
         self._sharded = False
         self.after_group = None     # optional callable(group index), called once a param group's kernels are enqueued
@@ -98,7 +100,12 @@ class _AdafacFamily(Optimizer):
             tensors.append(LoTensor(
                 p=p.data, m=st["exp_avg"], v=st["exp_avg_sq"], fac_r=st["exp_avg_sq_r"], fac_c=st["exp_avg_sq_c"],
                 fdims=fd, rcm_axis=axis, w=self._w_flat, peer_ptrs=getattr(p, "_pylo_peer_ptrs", None)))
-        return LoPlan(L.FAM_ADAFAC, tensors, self.device)
+        return LoPlan(L.FAM_ADAFAC, tensors, self.device, tensor_cores=self.mlp_precision == "3xtf32")
+
+    def check_status(self):
+        """Synchronise and raise if a tensor-core launch of an earlier step reported a timed-out wait."""
+        for _, plan in self._plans.values():
+            plan.check_status()
 
     def _run_group(self, gi, group, plist, prm, lr, wd, exp_mult, step_mult, clip_norm, stream):
         sig = tuple(p.data_ptr() for p in plist)
@@ -152,7 +159,8 @@ class AdafacLO_CUDA(_AdafacFamily):
                  weight_decay: float = 0.0, clipping_threshold: Optional[float] = None,
                  max_grad_norm: Optional[float] = None, unscaled_wd: bool = False, step_mult: float = 0.01,
                  exp_mult: float = 0.001, load_from_file: Optional[str] = None, *, foreach: Optional[bool] = False,
-                 hf_key: Optional[str] = "btherien/mulo", network: Optional[MetaMLP] = None):
+                 hf_key: Optional[str] = "btherien/mulo", network: Optional[MetaMLP] = None,
+                 mlp_precision: str = "fp32"):
         if isinstance(momentum_dtype, str):
             momentum_dtype = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}[momentum_dtype]
         if momentum_dtype != torch.float32:
@@ -189,6 +197,7 @@ class AdafacLO_CUDA(_AdafacFamily):
         self.beta_rms = reparam(initial_rms_decays, rms_decays)
         self.beta_adafactor = reparam(initial_adafactor_decays, adafactor_decays)
         self.step_mult, self.exp_mult = step_mult, exp_mult
+        self.mlp_precision = mlp_precision
         self._finish_init(self.metamlp)
 
     def __setstate__(self, state):
@@ -231,7 +240,7 @@ class ELO_CUDA(_AdafacFamily):
                  initial_momentum_decays=(0.9, 0.99, 0.999), initial_rms_decays=(0.999,),
                  initial_adafactor_decays=(0.9, 0.99, 0.999), clip_grad=False, clip_norm=1.0,
                  hf_key: Optional[str] = "DiamondXL/elo", checkpoint_path: Optional[str] = None,
-                 network: Optional[MetaMLP] = None):
+                 network: Optional[MetaMLP] = None, mlp_precision: str = "fp32"):
         if not torch.cuda.is_available():
             raise RuntimeError("ELO_CUDA requires a CUDA device.")
         self.device = torch.device("cuda")
@@ -252,6 +261,7 @@ class ELO_CUDA(_AdafacFamily):
         self.network = self.network.to(dev)
         for prm in self.network.parameters():
             prm.requires_grad = False
+        self.mlp_precision = mlp_precision
         self._finish_init(self.network)
 
     @torch.no_grad()

@@ -124,8 +124,9 @@ class LoPlan:
 
     H = {L.FAM_ADAFAC: 32, L.FAM_CELO2: 8, L.FAM_VELO: 4}
 
-    def __init__(self, family: int, tensors: List[LoTensor], device):
+    def __init__(self, family: int, tensors: List[LoTensor], device, tensor_cores: bool = False):
         self.family = family
+        self.tensor_cores = bool(tensor_cores) and family == L.FAM_ADAFAC
         self.tensors = tensors
         self.device = torch.device(device)
         T = len(tensors)
@@ -261,7 +262,13 @@ class LoPlan:
             if tdesc["mode"][i] != L.MODE_FAST2D:
                 continue
             X, Y = int(tdesc["X"][i]), int(tdesc["Y"][i])
-            if family == L.FAM_ADAFAC:
+            if self.tensor_cores:
+                # tensor-core kernel: items of 128 columns; rows per item as long as possible (the column terms are
+                # loaded once per item) while the tensor still yields >= 8 items per SM
+                ncol = (Y + 127) // 128
+                rt = next((r for r in (64, 32, 16) if ((X + r - 1) // r) * ncol >= 1184), 8)
+                width, tag = 128, rt
+            elif family == L.FAM_ADAFAC:
                 cw = min((256, 128, 64, 32), key=lambda c: ((Y + c - 1) // c * c - Y, -c))
                 ncol = (Y + cw - 1) // cw
                 # a work item is n_sub sub-tiles of 32 rows in one column block (the column terms are loaded
@@ -276,6 +283,8 @@ class LoPlan:
                     ctiles.append((unit_of[i], rtile, ctile, tag))
         self.ctiles = DeviceTable(np.array(ctiles, dtype=np.int32).reshape(-1, 4).view(L.ATILE_DTYPE).reshape(-1), self.device)
         self.n_ctiles = len(ctiles)
+        #: device flag the tensor-core kernel raises when one of its bounded waits ran out
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device) if self.tensor_cores else None
         fast_unit = udesc["mode"] == L.MODE_FAST2D
         slow = tiles[~fast_unit[tiles["tensor"]]] if len(tiles) else tiles
         self.tiles_slow = DeviceTable(np.ascontiguousarray(slow), self.device)
@@ -352,13 +361,23 @@ class LoPlan:
 
     def run_back(self, prm: L.StepParams, stream: int, reverse_c: bool = False):
         """Phases P, C."""
+        prm.no_tables = int(self.tensor_cores)
         pp = C.byref(prm)
         self._call("prep_apply", L.lib.pylo_b200_prep_apply, self.desc.ptr, self.n_units, pp, stream)
-        if self.n_ctiles:
+        if self.n_ctiles and self.tensor_cores:
+            self._call("apply_cols", L.lib.pylo_b200_apply_adafac_tc, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp,
+                       self.status.data_ptr(), stream)
+        elif self.n_ctiles:
             fn = L.lib.pylo_b200_apply_adafac_cols if self.family == L.FAM_ADAFAC else L.lib.pylo_b200_apply_packed
             self._call("apply_cols", fn, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp, stream)
         if self.n_tiles_slow:
             self._call("apply", L.lib.pylo_b200_apply, self.desc.ptr, self.tiles_slow.ptr, self.n_tiles_slow, int(reverse_c), pp, stream)
+
+
+    def check_status(self):
+        """Synchronise and raise if the tensor-core kernel reported a wait that ran out (its results are invalid)."""
+        if self.status is not None and int(self.status.item()) != 0:
+            raise L.PyloLibError("apply_adafac_tc: a wait on the tensor core timed out; this step's parameters are invalid")
 
 
 class GradNorm:
