@@ -37,7 +37,11 @@ APPLY_BYTES = 28
 B_BYTES = 40  # state_moments sweep: reads g, p, m(3), v; writes m(3), v
 # DRAM bytes per element (dram__bytes_read.sum + dram__bytes_write.sum) of each dominant kernel, from ncu
 # captures of a 4096 x 4096 case (profiles/*.md); traffic grows in proportion to the elements processed
-NCU_TRAFFIC_PER_ELEM = {("adafaclo", "apply_cols"): 27.58, ("elo", "apply_cols"): 27.58}
+NCU_TRAFFIC_PER_ELEM = {("adafaclo", "apply_cols", "fp32"): 27.58, ("elo", "apply_cols", "fp32"): 27.58,
+                        ("adafaclo", "apply_cols", "3xtf32"): 27.52, ("elo", "apply_cols", "3xtf32"): 27.52}
+# the tensor-core apply kernel issues 25 TF32 products of 128 x 32 x 8 per 128 parameters (two layers, three
+# products each for the high/low split, K padded to 32, one bias product)
+TC_ISSUED_FMA_PER_PARAM = 25 * 32 * 8
 
 
 def parse():
@@ -52,6 +56,9 @@ def parse():
     ap.add_argument("--no-orthogonalize", action="store_true", help="celo2 family: skip Newton-Schulz")
     ap.add_argument("--ns-precision", default="fp32", choices=["fp32", "3xtf32"],
                     help="celo2 family: Newton-Schulz products in fp32 (reference arithmetic) or as three TF32 tensor-core GEMMs")
+    ap.add_argument("--mlp-precision", default="3xtf32", choices=["fp32", "3xtf32"],
+                    help="adafaclo / elo: the network's hidden layers as scalar fp32 FMAs or as split-TF32 tensor-core "
+                         "products (fp32-faithful: three products per layer)")
     ap.add_argument("--blocks", type=int, default=8, help="N>1: stages whose parameter all-gathers overlap the next stage")
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "staged"],
                     help="N>1: how updated parameters reach the other ranks (peer stores fused into the apply kernels, "
@@ -110,9 +117,11 @@ def build_optimizer(args, shard, params):
     # let group k compute while the gradients of group k+1 are still arriving from the host
     groups = shard.param_groups(groups=args.blocks) if isinstance(shard, FusedShardedStep) else shard.param_groups()
     if k == "adafaclo":
-        opt = optim.AdafacLO_CUDA(groups, lr=1e-3, step_mult=0.01, exp_mult=0.001, network=seeded_networks(k))
+        opt = optim.AdafacLO_CUDA(groups, lr=1e-3, step_mult=0.01, exp_mult=0.001, network=seeded_networks(k),
+                                  mlp_precision=args.mlp_precision)
     elif k == "elo":
-        opt = optim.ELO_CUDA(groups, lr=1e-3, weight_decay=0.1, clip_grad=True, network=seeded_networks(k))
+        opt = optim.ELO_CUDA(groups, lr=1e-3, weight_decay=0.1, clip_grad=True, network=seeded_networks(k),
+                             mlp_precision=args.mlp_precision)
     else:
         cls = optim.CELO2_CUDA if k == "celo2" else optim.ELO_CELO2_CUDA
         opt = cls(shard.param_groups(is_embedding_shape), lr=1e-3, weight_decay=0.1,
@@ -222,6 +231,7 @@ def config_of(args, shapes, n_gpus):
         "optimizer": args.optimizer, "shapes": args.workload, "tensors": len(shapes),
         "params": W.total_params(shapes), "grads": f"randn*{gscale} ({gkind}), one buffer per distinct shape",
         "orthogonalize": (not args.no_orthogonalize) if "celo2" in args.optimizer else None,
+        "mlp_precision": args.mlp_precision if args.optimizer in ("adafaclo", "elo") else None,
         "cache": "inputs larger than L2 (no flush needed)" if W.total_params(shapes) * 24 / max(n_gpus, 1) > 2e9
                  else "L2 flushed between steps by writing a 512 MiB buffer",
         "parallelism": f"zero1x{n_gpus}", "exchange": getattr(args, "exchange_used", "none"),
@@ -354,6 +364,8 @@ def run_b200(args):
     ev[1].record()
     barrier()
     elapsed_ms = ev[0].elapsed_time(ev[1])
+    if hasattr(opt, "check_status"):
+        opt.check_status()  # raises if a bounded wait of the tensor-core kernel ran out during the timed steps
     clocks = sampler.stop() if rank == 0 else None
     phase = {}
     launches = 0
@@ -437,8 +449,8 @@ def run_b200(args):
         roofline = {
             "bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
             "frac": achieved / peak, "peak_source": f"{peak_src} (MEASURED_PEAKS.json hbm_gbs)",
-            "traffic": (NCU_TRAFFIC_PER_ELEM[(args.optimizer, dominant)] * per_launch_elems
-                        if (args.optimizer, dominant) in NCU_TRAFFIC_PER_ELEM else None),
+            "traffic": (NCU_TRAFFIC_PER_ELEM[(args.optimizer, dominant, args.mlp_precision)] * per_launch_elems
+                        if (args.optimizer, dominant, args.mlp_precision) in NCU_TRAFFIC_PER_ELEM else None),
             "traffic_note": "ncu dram bytes per element of a 4096x4096 capture x elements per launch",
             "algorithmic_bytes_per_param": kbytes, "avg_launch_ms": phase_ms.get(dominant),
             "phase_ms_per_launch": phase_ms,
@@ -446,7 +458,13 @@ def run_b200(args):
                      "achieved": owned_n * STEP_BYTES[args.optimizer] / (ms_per_step * 1e-3) / 1e9,
                      "frac": owned_n * STEP_BYTES[args.optimizer] / (ms_per_step * 1e-3) / 1e9 / peak},
         }
-        if args.optimizer in ("adafaclo", "elo") and dominant in ("apply", "apply_cols") and clocks and clocks.get("sm_mhz"):
+        if args.optimizer in ("adafaclo", "elo") and dominant == "apply_cols" and args.mlp_precision == "3xtf32":
+            # the tensor-core apply sweep is bound by the issue latency of its small (N = 32) products
+            issued = per_launch_elems * TC_ISSUED_FMA_PER_PARAM * 2 / (phase_ms[dominant] * 1e-3)
+            roofline["tensor"] = {"network_fma_per_param": 1600, "issued_tf32_fma_per_param": TC_ISSUED_FMA_PER_PARAM,
+                                  "issued_tf32_tflops": issued / 1e12,
+                                  "network_fp32_equiv_tflops": per_launch_elems * 3200 / (phase_ms[dominant] * 1e-3) / 1e12}
+        elif args.optimizer in ("adafaclo", "elo") and dominant in ("apply", "apply_cols") and clocks and clocks.get("sm_mhz"):
             # the apply sweep of the 39-32-32-2 network is bound by fp32 FMA issue, not by HBM
             fma = per_launch_elems * 1600 / (phase_ms[dominant] * 1e-3)
             peak_fma = 148 * 128 * clocks["sm_mhz"] * 1e6

@@ -237,8 +237,8 @@ int pylo_b200_apply_adafac_cols(const pylo_tensor_desc* descs, const pylo_atile*
  * and outputs as pylo_b200_apply_adafac_cols; the two hidden layers run as tcgen05 TF32 products with every
  * operand split into a high and a low TF32 part (three products per layer), which keeps a 32-term dot product
  * within ~3e-7 of the sum of its terms' magnitudes; non-finite features give NaN where the scalar path may give
- * an infinity.  ttiles: strip = row-strip index, cb = block of 128 columns, pad_ = rows per work item (a multiple
- * of 4).  status: device int the kernel ORs 1 into if a wait on the tensor core ran out (results are then
+ * an infinity.  ttiles: strip = row-strip index, cb = block of 128 columns, pad_ = rows per work item (one
+ * warpgroup of a CTA takes a whole item).  status: device int the kernel ORs 1 into if a wait on the tensor core ran out (results are then
  * invalid); may be NULL. */
 int pylo_b200_apply_adafac_tc(const pylo_tensor_desc* descs, const pylo_atile* ttiles, int n_ttiles,
                               const pylo_step_params* prm, int* status, void* stream);

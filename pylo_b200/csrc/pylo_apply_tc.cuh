@@ -17,12 +17,16 @@
 //     split the same way, rebuilt only when the CTA moves to another tensor;
 //   * relu, the split of the hidden activations, the two output heads and the parameter update
 //     stay on the CUDA cores, which work on one warpgroup's tile while the tensor core works on
-//     another's: four warpgroups per CTA, one CTA per SM, each with its own accumulator columns.
+//     another's: four warpgroups per CTA, one CTA per SM; every warpgroup is an independent worker
+//     with its own work items, its own copy of the weights in shared memory, its own accumulator
+//     columns and its own barriers, so the warpgroups drift apart instead of marching in step.
 // Every wait on the tensor core is bounded: on a timeout the kernel records it in *status and goes on
 // (with wrong values) to the end, where it frees its tensor memory.
 #pragma once
 
+#ifndef TC_WGS
 #define TC_WGS 4                 // warpgroups per CTA
+#endif
 #define TC_NT (TC_WGS * 128)
 #define TC_COLS 128              // tensor columns per work item: one per lane of the accumulator tile
 #define TC_WG_TMEM 128           // tensor-memory columns per warpgroup: [0,64) operand A, [64,96) accumulator, [96,104) constant
@@ -95,16 +99,45 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t saddr) {
 // instruction descriptor: fp32 accumulate, TF32 x TF32, both operands K-major, N = 32, M = 128
 constexpr uint32_t TC_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((32u >> 3) << 17) | ((128u >> 4) << 24);
 
+// read-only 128-bit load issued where it is written (the compiler would otherwise sink it to its first use)
+__device__ __forceinline__ float4 ldg4_early(const float* p) {
+  float4 v;
+  asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+
 __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
 
-struct TcSmem {
+// per-item constants; they are read back from shared memory at their points of use (volatile, so that the
+// compiler does not hoist them into registers for the whole row loop: at 512 threads a thread has 128 registers)
+struct TcItem {
+  const float* g;
+  float* p;
+  const float* m;
+  const float* v;
+  const float* fx;
+  const float* fac_a;
+  float* const* peer;
+  long long n;
+  float exp_mult, step_mult, wd, lr, lr_eff, gs;
+  int wd_mode, n_peer;
+};
+
+// One warpgroup's private shared memory: its copy of the weights, the vector features of its item's columns and
+// of its row in flight, its item constants and its tensor-core barrier.  Warpgroups never wait on one another.
+struct TcWgSmem {
   float b1hi[32 * 32], b1lo[32 * 32];            // first layer: N = 32, K = 32 (28 features, bias row, 3 zero rows)
   float b2hi[32 * 32], b2lo[32 * 32];            // second layer: N = 32, K = 32
   float b2bias[32 * 8];                          // second-layer bias as a K = 8 block: (high part, low part, 0 ...)
-  float w[Fold<PYLO_FAM_ADAFAC>::SIZE + 12];     // folded network (the output layer is read from here)
+  float w3[64 + 4];                              // output layer, pair-major (Fold::W3P), then its two biases
   float4 colf[3][TC_COLS];                       // the item's columns: 6 vector features, high parts then low parts
-  float4 rowf[TC_WGS][2][3];                     // per warpgroup, double-buffered: the same for the row in flight / the next
-  uint64_t bar[TC_WGS];
+  float4 rowf[2][4];                             // double-buffered: the same for the row in flight / the next, then the
+                                                 // row's three factors of the element-wise factored features
+  TcItem item;
+  uint64_t bar;
+};
+struct TcSmem {
+  TcWgSmem wg[TC_WGS];
   uint32_t tmem_base;
 };
 
@@ -126,15 +159,16 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
   using F = Fam<PYLO_FAM_ADAFAC>;
   using L = Fold<PYLO_FAM_ADAFAC>;
   extern __shared__ __align__(128) unsigned char tc_raw[];
-  TcSmem& sm = *reinterpret_cast<TcSmem*>(tc_raw);
+  TcSmem& smem = *reinterpret_cast<TcSmem*>(tc_raw);
   const int tid = threadIdx.x, warp = tid >> 5, wg = tid >> 7, col = tid & 127;
-  if (tid < TC_WGS) mbar_init(&sm.bar[tid], 1);
+  TcWgSmem& sm = smem.wg[wg];
+  if (col == 0) mbar_init(&sm.bar, 1);
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  if (warp == 0) { tc_alloc(&sm.tmem_base, 512); tc_relinquish(); }
+  if (warp == 0) { tc_alloc(&smem.tmem_base, 512); tc_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t t_wg = sm.tmem_base + wg * TC_WG_TMEM;                 // lane 0 of this warpgroup's columns
+  const uint32_t t_wg = smem.tmem_base + wg * TC_WG_TMEM;               // lane 0 of this warpgroup's columns
   const uint32_t t_lane = t_wg + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes
   const uint32_t tA = t_lane, tD = t_lane + 64;
   {  // columns [96,104): a constant operand (1, 1, 0 ...) that adds the second-layer bias as one more product
@@ -143,29 +177,27 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
                  ::"r"(t_lane + 96), "r"(one[0]), "r"(one[1]), "r"(one[2]), "r"(one[3]), "r"(one[4]), "r"(one[5]), "r"(one[6]), "r"(one[7]) : "memory");
     tc_wait_st();
   }
-  const uint64_t desc_b1hi = tc_desc(smem_addr(sm.b1hi)), desc_b1lo = tc_desc(smem_addr(sm.b1lo));
-  const uint64_t desc_b2hi = tc_desc(smem_addr(sm.b2hi)), desc_b2lo = tc_desc(smem_addr(sm.b2lo));
-  const uint64_t desc_b2bias = tc_desc(smem_addr(sm.b2bias));
   constexpr uint64_t KSTEP = (2 * TC_LBO) >> 4;  // one product consumes two K chunks
   uint32_t parity = 0;
   bool timed_out = false;
   int loaded = -1;
-  for (int t = blockIdx.x; t < n_ttiles; t += gridDim.x) {
+  // every warpgroup is a worker of its own: it takes every (gridDim.x * TC_WGS)-th work item
+  for (int t = blockIdx.x * TC_WGS + wg; t < n_ttiles; t += gridDim.x * TC_WGS) {
     const pylo_atile ct = ttiles[t];
     const pylo_tensor_desc& d = descs[ct.tensor];
     const int X = d.X, Y = d.Y;
-    const int rows_item = ct.pad_;  // rows per work item, a multiple of TC_WGS
+    const int rows_item = ct.pad_;  // rows per work item
     const int y = ct.cb * TC_COLS + col;
     const bool colok = y < Y;
     const int yc = colok ? y : 0;
     const int x0 = ct.strip * rows_item;
-    __syncthreads();  // every warpgroup is done with the previous item's column terms and weights
+    wg_barrier(wg);  // the four warps are done with the previous item's column terms and weights
     if (loaded != ct.tensor) {
       // K order of the first layer: 16 element-wise features (0..12, 25..27), the six features of the row vector,
       // the six of the column vector, the bias (against a constant 1), three zero rows
       const int ka = d.r_is_a ? F::R : F::C, kra = d.r_is_a ? F::RR : F::RC;
       const int kb = d.r_is_a ? F::C : F::R, krb = d.r_is_a ? F::RC : F::RR;
-      for (int e = tid; e < 32 * 32; e += TC_NT) {
+      for (int e = col; e < 32 * 32; e += 128) {
         const int n = e & 31, kk = e >> 5;
         float w = 0.f;
         if (kk < 13) w = d.wfold[L::W1 + kk * 32 + n];
@@ -179,62 +211,76 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
         sm.b1hi[tc_b_index(n, kk)] = hi;
         sm.b1lo[tc_b_index(n, kk)] = w - hi;
       }
-      for (int e = tid; e < 32 * 32; e += TC_NT) {
+      for (int e = col; e < 32 * 32; e += 128) {
         const int n = e & 31, k = e >> 5;
         const float w = d.wfold[L::W2 + k * 32 + n], hi = tf32_hi(w);
         sm.b2hi[tc_b_index(n, k)] = hi;
         sm.b2lo[tc_b_index(n, k)] = w - hi;
       }
-      for (int e = tid; e < 32 * 8; e += TC_NT) {
+      for (int e = col; e < 32 * 8; e += 128) {
         const int n = e & 31, k = e >> 5;
         const float w = d.wfold[L::B2 + n], hi = tf32_hi(w);
         sm.b2bias[tc_b_index(n, k)] = k == 0 ? hi : (k == 1 ? w - hi : 0.f);
       }
-      for (int e = tid; e < L::SIZE; e += TC_NT) sm.w[e] = d.wfold[e];
+      if (col < 64) sm.w3[col] = d.wfold[L::W3P + col];
+      if (col < 2) sm.w3[64 + col] = d.wfold[L::B3 + col];
       loaded = ct.tensor;
     }
-    for (int e = tid; e < 6 * TC_COLS; e += TC_NT) {
+    for (int e = col; e < 6 * TC_COLS; e += 128) {
       const int j = e / TC_COLS, c = e % TC_COLS, yy = ct.cb * TC_COLS + c;
       const float v = yy < Y ? tc_vec_feature(d.fac_b, Y, yy, j) : 0.f;
       const float hi = tf32_hi(v);
       reinterpret_cast<float*>(&sm.colf[j >> 2][c])[j & 3] = hi;
       reinterpret_cast<float*>(&sm.colf[(6 + j) >> 2][c])[(6 + j) & 3] = v - hi;
     }
-    if (col < 6 && x0 + wg < X) tc_put6(&sm.rowf[wg][0][0], col, tc_vec_feature(d.fac_a, X, x0 + wg, col));
+    if (col < 6 && x0 < X) tc_put6(&sm.rowf[0][0], col, tc_vec_feature(d.fac_a, X, x0, col));
+    if (col >= 6 && col < 9 && x0 < X) reinterpret_cast<float*>(&sm.rowf[0][3])[col - 6] = d.fx[(int64_t)x0 * 4 + (col - 6)];
+    if (col == 0) {
+      TcItem& it = sm.item;
+      it.g = d.g; it.p = d.p; it.m = d.m; it.v = d.v; it.fx = d.fx; it.fac_a = d.fac_a;
+      it.peer = d.p_peer; it.n_peer = d.n_peer; it.n = d.n;
+      it.exp_mult = d.exp_mult; it.step_mult = d.step_mult; it.wd = d.wd; it.lr = d.lr;
+      it.lr_eff = d.wfold[L::SC + 1]; it.gs = grad_scale_of(d, prm); it.wd_mode = prm.wd_mode;
+    }
     fence_async_smem();  // the tensor core reads the weights through the async proxy
-    __syncthreads();
+    wg_barrier(wg);
     const float fb0 = d.f_b[yc], fb1 = d.f_b[Y + yc], fb2 = d.f_b[2 * (int64_t)Y + yc];
-    const float gs = grad_scale_of(d, prm);
-    const int64_t n = d.n;
-    const float* __restrict__ gp = d.g;
-    float* __restrict__ pp = d.p;
-    const float* __restrict__ mp = d.m;
-    const float* __restrict__ vp = d.v;
-    const Peers peers = load_peers(d);
-    const Fin fin = make_fin(d, 1.0f, sm.w[L::SC + 1], prm.wd_mode);
+    const volatile TcItem& ic = sm.item;
     float cg, cp, cm0, cm1, cm2, cv;
-    float4 cfa;
-    auto load_row = [&](int x, float& g, float& p, float& m0, float& m1, float& m2, float& v, float4& fa) {
-      const int xs = x < X ? x : 0;
+    auto load_row = [&](int x, float& g, float& p, float& m0, float& m1, float& m2, float& v) {
       const int64_t idx = (colok && x < X) ? (int64_t)x * Y + y : 0;
-      g = ldg_early(gp + idx); p = ldg_early(pp + idx); m0 = ldg_early(mp + idx);
-      m1 = ldg_early(mp + n + idx); m2 = ldg_early(mp + 2 * n + idx); v = ldg_early(vp + idx);
-      fa = __ldg(reinterpret_cast<const float4*>(d.fx + (int64_t)xs * 4));
+      const int64_t n = ic.n;
+      const float* mp = ic.m;
+      g = ldg_early(ic.g + idx); p = ldg_early(ic.p + idx); m0 = ldg_early(mp + idx);
+      m1 = ldg_early(mp + n + idx); m2 = ldg_early(mp + 2 * n + idx); v = ldg_early(ic.v + idx);
     };
-    load_row(x0 + wg, cg, cp, cm0, cm1, cm2, cv, cfa);
+    load_row(x0, cg, cp, cm0, cm1, cm2, cv);
+    // threads 0..8 carry one row-wide value for the row after next: the row vector's factor (0..5) or one of the
+    // row's three factors (6..8); one global load each, consumed an iteration later, so that its latency never sits
+    // between two barriers
+    auto load_fac = [&](int x) {
+      const float* src = ic.fac_a;
+      int64_t off = 0;
+      if (x < X) {
+        if (col < 6) off = (int64_t)(col % 3) * X + x;
+        else if (col < 9) { src = ic.fx; off = (int64_t)x * 4 + (col - 6); }
+      }
+      return ldg_early(src + off);
+    };
+    float fac_next = load_fac(x0 + 1);
 #pragma unroll 1
-    for (int i = 0; i * TC_WGS < rows_item; ++i) {
-      const int x = x0 + i * TC_WGS + wg;  // the same for the whole warpgroup
+    for (int i = 0; i < rows_item; ++i) {
+      const int x = x0 + i;  // the same for the whole warpgroup
       if (x >= X) break;
-      float ng_, np_, nm0, nm1, nm2, nv;
-      float4 nfa;
-      load_row(x + TC_WGS, ng_, np_, nm0, nm1, nm2, nv, nfa);
-      // the next row's vector features, for the next iteration (two warpgroup barriers lie in between)
-      if (col < 6 && x + TC_WGS < X) tc_put6(&sm.rowf[wg][(i + 1) & 1][0], col, tc_vec_feature(d.fac_a, X, x + TC_WGS, col));
+      // the next row's row-wide values, for the next iteration (two warpgroup barriers lie in between)
+      if (col < 6) tc_put6(&sm.rowf[(i + 1) & 1][0], col, col < 3 ? fac_next : rsqrtf(fac_next + 1e-8f));
+      else if (col < 9) reinterpret_cast<float*>(&sm.rowf[(i + 1) & 1][3])[col - 6] = fac_next;
+      fac_next = load_fac(x + 2);
       // ---- operand A of the first layer, high and low parts
       {
-        const float g = xform_grad(cg, gs, prm.clip_val, prm.nan_to_num);
+        const float g = xform_grad(cg, ic.gs, prm.clip_val, prm.nan_to_num);
         const float rs = rsqrt_pos(cv + prm.eps_feat);
+        const float4 cfa = sm.rowf[i & 1][3];
         const float k0 = cfa.x * fb0, k1 = cfa.y * fb1, k2 = cfa.z * fb2;
         const float fe[16] = {g, cp, cm0, cm1, cm2, cv, cm0 * rs, cm1 * rs, cm2 * rs, rs,
                               k0 * g, k1 * g, k2 * g, k0 * cm0, k1 * cm1, k2 * cm2};
@@ -247,7 +293,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
         }
         tc_st16(tA, hi);
         tc_st16(tA + 32, lo);
-        const float4 r0 = sm.rowf[wg][i & 1][0], r1 = sm.rowf[wg][i & 1][1], r2 = sm.rowf[wg][i & 1][2];
+        const float4 r0 = sm.rowf[i & 1][0], r1 = sm.rowf[i & 1][1], r2 = sm.rowf[i & 1][2];
         const float4 c0 = sm.colf[0][col], c1 = sm.colf[1][col], c2 = sm.colf[2][col];
         // (r0, r1.xy) = row high parts, (r1.zw, r2) = row low parts; the same for the column
         const uint32_t vhi[16] = {__float_as_uint(r0.x), __float_as_uint(r0.y), __float_as_uint(r0.z), __float_as_uint(r0.w),
@@ -261,21 +307,26 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
         tc_st16(tA + 16, vhi);
         tc_st16(tA + 48, vlo);
       }
+      // the next row's operands: requested now that this row's are consumed (only p is still needed, for the
+      // update), so the two sets never share the register file; they land during the two products
+      float np_;
+      load_row(x + 1, cg, np_, cm0, cm1, cm2, cv);
       tc_wait_st();
       tc_fence_before();
       wg_barrier(wg);
       if (col == 0) {
         tc_fence_after();
+        const uint64_t desc_b1hi = tc_desc(smem_addr(sm.b1hi)), desc_b1lo = tc_desc(smem_addr(sm.b1lo));
 #pragma unroll
         for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 32 + 8 * s, desc_b1hi + s * KSTEP, TC_IDESC, s > 0);  // lo x hi
 #pragma unroll
         for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 8 * s, desc_b1lo + s * KSTEP, TC_IDESC, 1);           // hi x lo
 #pragma unroll
         for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 8 * s, desc_b1hi + s * KSTEP, TC_IDESC, 1);           // hi x hi
-        tc_commit(&sm.bar[wg]);
+        tc_commit(&sm.bar);
       }
       __syncwarp();
-      if (!mbar_wait(&sm.bar[wg], parity)) timed_out = true;
+      if (!mbar_wait(&sm.bar, parity)) timed_out = true;
       parity ^= 1;
       tc_fence_after();
       // ---- hidden layer 1: relu, split, back into tensor memory as operand A of the second layer
@@ -298,6 +349,8 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
       wg_barrier(wg);
       if (col == 0) {
         tc_fence_after();
+        const uint64_t desc_b2hi = tc_desc(smem_addr(sm.b2hi)), desc_b2lo = tc_desc(smem_addr(sm.b2lo));
+        const uint64_t desc_b2bias = tc_desc(smem_addr(sm.b2bias));
         tc_mma(t_wg + 64, t_wg + 96, desc_b2bias, TC_IDESC, 0);                                                    // bias
 #pragma unroll
         for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 32 + 8 * s, desc_b2hi + s * KSTEP, TC_IDESC, 1);      // lo x hi
@@ -305,10 +358,10 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
         for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 8 * s, desc_b2lo + s * KSTEP, TC_IDESC, 1);           // hi x lo
 #pragma unroll
         for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 8 * s, desc_b2hi + s * KSTEP, TC_IDESC, 1);           // hi x hi
-        tc_commit(&sm.bar[wg]);
+        tc_commit(&sm.bar);
       }
       __syncwarp();
-      if (!mbar_wait(&sm.bar[wg], parity)) timed_out = true;
+      if (!mbar_wait(&sm.bar, parity)) timed_out = true;
       parity ^= 1;
       tc_fence_after();
       // ---- hidden layer 2 (relu) and the two output heads as packed dot products over unit pairs
@@ -320,7 +373,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
         tc_wait_ld();
 #pragma unroll
         for (int jp = 0; jp < 8; ++jp) {
-          const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(&sm.w[L::W3P + 4 * (half * 8 + jp)]);  // (dir pair, mag pair)
+          const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(&sm.w3[4 * (half * 8 + jp)]);  // (dir pair, mag pair)
           const uint64_t r = pack2(fmaxf(__uint_as_float(dv[2 * jp]), 0.f), fmaxf(__uint_as_float(dv[2 * jp + 1]), 0.f));
           od[jp & 1] = fma2(w.x, r, od[jp & 1]);
           om[jp & 1] = fma2(w.y, r, om[jp & 1]);
@@ -330,18 +383,20 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
         float a, b, c, dd;
         unpack2(add2(od[0], od[1]), a, b);
         unpack2(add2(om[0], om[1]), c, dd);
-        const float o0 = (a + b) + sm.w[L::B3], o1 = (c + dd) + sm.w[L::B3 + 1];
+        const float o0 = (a + b) + sm.w3[64], o1 = (c + dd) + sm.w3[65];
         if (colok) {
+          const Fin fin{ic.exp_mult, ic.step_mult, ic.wd, ic.lr, ic.lr_eff, 1.0f, ic.wd_mode};
           const float pn = finish<PYLO_FAM_ADAFAC>(cp, o0, o1, fin);
-          pp[(int64_t)x * Y + y] = pn;
-          peer_store(peers, (int64_t)x * Y + y, pn);
+          const int64_t idx = (int64_t)x * Y + y;
+          ic.p[idx] = pn;
+          peer_store(Peers{ic.peer, ic.n_peer}, idx, pn);
         }
       }
-      cg = ng_; cp = np_; cm0 = nm0; cm1 = nm1; cm2 = nm2; cv = nv; cfa = nfa;
+      cp = np_;
     }
   }
   if (timed_out && status) atomicOr(status, 1);
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tc_dealloc(sm.tmem_base, 512);
+  if (warp == 0) tc_dealloc(smem.tmem_base, 512);
 }

@@ -263,10 +263,11 @@ class LoPlan:
                 continue
             X, Y = int(tdesc["X"][i]), int(tdesc["Y"][i])
             if self.tensor_cores:
-                # tensor-core kernel: items of 128 columns; rows per item as long as possible (the column terms are
-                # loaded once per item) while the tensor still yields >= 8 items per SM
+                # tensor-core kernel: an item is rt rows x 128 columns, taken by one warpgroup (4 per SM); rows per
+                # item as many as possible (the column terms are loaded once per item) while the tensor still yields
+                # >= 8 items per warpgroup
                 ncol = (Y + 127) // 128
-                rt = next((r for r in (64, 32, 16) if ((X + r - 1) // r) * ncol >= 1184), 8)
+                rt = next((r for r in (64, 32, 16) if ((X + r - 1) // r) * ncol >= 8 * 592), 8)
                 width, tag = 128, rt
             elif family == L.FAM_ADAFAC:
                 cw = min((256, 128, 64, 32), key=lambda c: ((Y + c - 1) // c * c - Y, -c))
@@ -284,7 +285,7 @@ class LoPlan:
         self.ctiles = DeviceTable(np.array(ctiles, dtype=np.int32).reshape(-1, 4).view(L.ATILE_DTYPE).reshape(-1), self.device)
         self.n_ctiles = len(ctiles)
         #: device flag the tensor-core kernel raises when one of its bounded waits ran out
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device) if self.tensor_cores else None
+        self.status = torch.zeros(64, dtype=torch.int32, device=self.device) if self.tensor_cores else None
         fast_unit = udesc["mode"] == L.MODE_FAST2D
         slow = tiles[~fast_unit[tiles["tensor"]]] if len(tiles) else tiles
         self.tiles_slow = DeviceTable(np.ascontiguousarray(slow), self.device)
@@ -376,7 +377,7 @@ class LoPlan:
 
     def check_status(self):
         """Synchronise and raise if the tensor-core kernel reported a wait that ran out (its results are invalid)."""
-        if self.status is not None and int(self.status.item()) != 0:
+        if self.status is not None and int(self.status[0].item()) != 0:
             raise L.PyloLibError("apply_adafac_tc: a wait on the tensor core timed out; this step's parameters are invalid")
 
 

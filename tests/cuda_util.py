@@ -6,11 +6,12 @@ import cases
 import golden_util as G
 
 
-def make_cuda_optimizer(case, weights, params):
+def make_cuda_optimizer(case, weights, params, **extra):
     import pylo_b200
     from pylo_b200 import models, optim
 
     fam, hp = case["family"], dict(case["hparams"])
+    hp.update(extra)  # e.g. mlp_precision="3xtf32"
     dev = params[0].device
     if fam in ("celo2", "elo_celo2"):
         net = models.CELO2MLP()
@@ -37,9 +38,9 @@ def make_cuda_optimizer(case, weights, params):
     raise ValueError(fam)
 
 
-def run_cuda(case, weights, record=None, device="cuda"):
+def run_cuda(case, weights, record=None, device="cuda", **extra):
     params = [torch.nn.Parameter(v.to(device)) for v in cases.init_values(case)]
-    opt = make_cuda_optimizer(case, weights, params)
+    opt = make_cuda_optimizer(case, weights, params, **extra)
     record = record or case["record"]
     out = {}
     for t in range(1, max(record) + 1):

@@ -1,0 +1,126 @@
+"""GPU checks of the tensor-core variant of the AdafacLO / ELO apply kernel (``mlp_precision="3xtf32"``).
+
+The two hidden layers run as tcgen05 TF32 products with every operand split into a high and a low part;
+the results must stay inside the same bounds as the scalar-FMA path: 1e-5 relative per element after one
+step, 1e-4 after the whole trajectory, movement within 2e-3 of its largest entry against the oracle, and
+within 1e-5 of the movement against the scalar-FMA path of the library itself at the full 4096 x 4096 size.
+"""
+
+import pytest
+import torch
+
+import cases
+import cuda_util as CU
+import golden_util as G
+
+pytestmark = pytest.mark.gpu
+
+TC = dict(mlp_precision="3xtf32")
+ADAFAC_CASES = sorted(n for n, c in G.CASES.items() if c["family"] in ("adafaclo", "elo"))
+
+
+def _net():
+    from pylo_b200 import models
+
+    torch.manual_seed(0)
+    return models.MetaMLP(39, 32, 1)
+
+
+def _make(family, params, **kw):
+    from pylo_b200 import optim
+
+    if family == "adafaclo":
+        return optim.AdafacLO_CUDA(params, lr=1e-2, network=_net(), **kw)
+    return optim.ELO_CUDA(params, lr=1e-2, weight_decay=0.1, clip_grad=True, network=_net(), **kw)
+
+
+@pytest.mark.parametrize("name", ADAFAC_CASES)
+def test_tensor_core_path_matches_oracle(name):
+    meta, weights, golden, _ = G.load(name)
+    case = G.CASES[name]
+    ref = G.run(case, G.make_oracle(case, weights, variant="cuda"))
+    got, opt, _ = CU.run_cuda(case, weights, **TC)
+    opt.check_status()
+    assert any(plan.tensor_cores and plan.n_ctiles for _, plan in opt._plans.values()), "no tensor took the tensor-core kernel"
+    res = CU.compare(got, ref, cases.init_values(case))
+    first, last = min(res), max(res)
+    assert res[first][0] < 1e-5, res
+    assert res[last][0] < 1e-4, res
+    assert all(r[1] < 2e-3 for r in res.values()), res
+
+
+# two-dimensional shapes that are factored (both sides >= 32) with ragged edges: columns that do not fill a
+# block of 128, fewer rows than one work item, a single block; plus tensors that stay on the generic kernel
+TC_RAGGED = [(257, 129), (129, 300), (64, 128), (33, 37), (40, 4100), (7,), (5, 3)]
+
+
+@pytest.mark.parametrize("family", ["adafaclo", "elo"])
+def test_tensor_core_ragged_shapes_match_oracle(family):
+    from oracle import pylo_oracle as O
+
+    case = dict(name="tc_ragged", family=family, shapes=TC_RAGGED, net_seed=0, init_seed=5, init_scale=0.1, grad_seed=6,
+                grad_scale=0.3, steps=3, record=[1, 3], hparams={})
+    params = [torch.nn.Parameter(v.cuda()) for v in cases.init_values(case)]
+    opt = _make(family, params, **TC)
+    kw = dict(lr=1e-2, elo=(family == "elo"))
+    if family == "elo":
+        kw.update(weight_decay=0.1, clip_grad=True)
+    ora = O.AdafacLOOracle(_net().flat_weights(), **kw)
+    ref = [v.clone() for v in cases.init_values(case)]
+    init = [v.clone() for v in ref]
+    for t in (1, 2, 3):
+        grads = cases.grads_at(case, t)
+        for p, g in zip(params, grads):
+            p.grad = g.cuda()
+        opt.step()
+        ora.step(ref, grads)
+    opt.check_status()
+    res = CU.compare({3: [p.detach().cpu() for p in params]}, {3: ref}, init)
+    assert res[3][0] < 1e-5 and res[3][1] < 2e-3, res
+
+
+@pytest.mark.parametrize("family,extra", [("adafaclo", {}), ("adafaclo", {"weight_decay": 0.1}), ("elo", {})])
+def test_tensor_core_and_fma_paths_agree_at_full_size(family, extra):
+    """4096 x 4096 and a 4096 x 1000 tensor (ragged last column block): the update through the tensor cores must
+    equal the scalar-FMA one to 1e-5 of the largest movement (a few ulp of the parameter are discounted)."""
+    shapes = [(4096, 4096), (4096, 1000)]
+    outs, init = {}, None
+    for prec in ("fp32", "3xtf32"):
+        gen = torch.Generator(device="cuda").manual_seed(3)
+        ps = [torch.nn.Parameter(torch.randn(*s, device="cuda", generator=gen) * 0.02) for s in shapes]
+        init = [p.detach().clone() for p in ps]
+        rows = [torch.exp(-7 + torch.randn(s[0], 1, device="cuda", generator=gen)) for s in shapes]
+        opt = _make(family, ps, mlp_precision=prec, **extra)
+        for t in (1, 2):
+            g = torch.Generator(device="cuda").manual_seed(100 + t)
+            for p, r in zip(ps, rows):
+                p.grad = torch.randn(*p.shape, device="cuda", generator=g) * r
+            opt.step()
+        opt.check_status()
+        outs[prec] = [p.detach().clone() for p in ps]
+    for a, b, w0 in zip(outs["fp32"], outs["3xtf32"], init):
+        moved = (a - w0).abs().max()
+        assert moved > 0
+        err = torch.clamp((a - b).abs() - 4 * 1.2e-7 * a.abs(), min=0).max()
+        assert float(err / moved) < 1e-5, float(err / moved)
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-7)
+
+
+def test_tensor_core_path_is_bit_reproducible():
+    outs = []
+    for _ in range(2):
+        gen = torch.Generator(device="cuda").manual_seed(3)
+        p = torch.nn.Parameter(torch.randn(2048, 4096, device="cuda", generator=gen) * 0.02)
+        opt = _make("adafaclo", [p], **TC)
+        for _ in range(2):
+            p.grad = torch.randn(2048, 4096, device="cuda", generator=gen) * 1e-3
+            opt.step()
+        opt.check_status()
+        outs.append(p.detach().clone())
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_unknown_mlp_precision_is_rejected():
+    p = torch.nn.Parameter(torch.zeros(64, 64, device="cuda"))
+    with pytest.raises(ValueError):
+        _make("adafaclo", [p], mlp_precision="bf16")
