@@ -13,6 +13,13 @@ than two dims use ``safe_rsqrt(v + 1e-9)`` for both factored features
 kernel indexes the factor vectors as if the tensor were 2-D
 (learned_optimizer.cu:70-86); here they are indexed by the element's true
 coordinates.
+
+``mlp_precision`` (an addition) selects how the network's two hidden layers are
+evaluated on factored 2-D tensors: ``"3xtf32"`` (default) as tcgen05 tensor-core
+products with every operand split into a high and a low TF32 part, three
+products per layer, which reproduces the fp32 result to ~3e-7 of a dot
+product's magnitude; ``"fp32"`` as scalar fp32 FMAs on the CUDA cores, the
+arithmetic of the reference kernel.  Both meet the same parity bounds.
 """
 
 from __future__ import annotations
@@ -160,7 +167,7 @@ class AdafacLO_CUDA(_AdafacFamily):
                  max_grad_norm: Optional[float] = None, unscaled_wd: bool = False, step_mult: float = 0.01,
                  exp_mult: float = 0.001, load_from_file: Optional[str] = None, *, foreach: Optional[bool] = False,
                  hf_key: Optional[str] = "btherien/mulo", network: Optional[MetaMLP] = None,
-                 mlp_precision: str = "fp32"):
+                 mlp_precision: str = "3xtf32"):
         if isinstance(momentum_dtype, str):
             momentum_dtype = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}[momentum_dtype]
         if momentum_dtype != torch.float32:
@@ -240,7 +247,7 @@ class ELO_CUDA(_AdafacFamily):
                  initial_momentum_decays=(0.9, 0.99, 0.999), initial_rms_decays=(0.999,),
                  initial_adafactor_decays=(0.9, 0.99, 0.999), clip_grad=False, clip_norm=1.0,
                  hf_key: Optional[str] = "DiamondXL/elo", checkpoint_path: Optional[str] = None,
-                 network: Optional[MetaMLP] = None, mlp_precision: str = "fp32"):
+                 network: Optional[MetaMLP] = None, mlp_precision: str = "3xtf32"):
         if not torch.cuda.is_available():
             raise RuntimeError("ELO_CUDA requires a CUDA device.")
         self.device = torch.device("cuda")

@@ -49,6 +49,19 @@ def test_tensor_core_path_matches_oracle(name):
     assert all(r[1] < 2e-3 for r in res.values()), res
 
 
+@pytest.mark.parametrize("name", ADAFAC_CASES)
+def test_scalar_fma_path_matches_oracle(name):
+    """The CUDA-core path (``mlp_precision="fp32"``) is no longer the default, so it is pinned here."""
+    meta, weights, golden, _ = G.load(name)
+    case = G.CASES[name]
+    ref = G.run(case, G.make_oracle(case, weights, variant="cuda"))
+    got, opt, _ = CU.run_cuda(case, weights, mlp_precision="fp32")
+    assert not any(plan.tensor_cores for _, plan in opt._plans.values())
+    res = CU.compare(got, ref, cases.init_values(case))
+    first, last = min(res), max(res)
+    assert res[first][0] < 1e-5 and res[last][0] < 1e-4 and all(r[1] < 2e-3 for r in res.values()), res
+
+
 # two-dimensional shapes that are factored (both sides >= 32) with ragged edges: columns that do not fill a
 # block of 128, fewer rows than one work item, a single block; plus tensors that stay on the generic kernel
 TC_RAGGED = [(257, 129), (129, 300), (64, 128), (33, 37), (40, 4100), (7,), (5, 3)]
