@@ -117,6 +117,7 @@ def _load():
 lib, EXPORTED = _load()
 
 
+TC_WORKERS = 148 * 5  # warpgroups the tensor-core apply kernel runs at once (5 per SM)
 STATIC_SCRATCH_TILES = 65536
 ERR_STATIC_SCRATCH_TOO_SMALL = -4
 

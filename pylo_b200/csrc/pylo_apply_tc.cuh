@@ -17,7 +17,7 @@
 //     split the same way, rebuilt only when the CTA moves to another tensor;
 //   * relu, the split of the hidden activations, the two output heads and the parameter update
 //     stay on the CUDA cores, which work on one warpgroup's tile while the tensor core works on
-//     another's: four warpgroups per CTA, one CTA per SM; every warpgroup is an independent worker
+//     another's: five warpgroups per CTA, one CTA per SM; every warpgroup is an independent worker
 //     with its own work items, its own copy of the weights in shared memory, its own accumulator
 //     columns and its own barriers, so the warpgroups drift apart instead of marching in step.
 // Every wait on the tensor core is bounded: on a timeout the kernel records it in *status and goes on
@@ -25,11 +25,12 @@
 #pragma once
 
 #ifndef TC_WGS
-#define TC_WGS 4                 // warpgroups per CTA
+#define TC_WGS 5                 // warpgroups per CTA: 5 x 96 tensor-memory columns + 8 shared ones fit the SM's 512
 #endif
 #define TC_NT (TC_WGS * 128)
 #define TC_COLS 128              // tensor columns per work item: one per lane of the accumulator tile
-#define TC_WG_TMEM 128           // tensor-memory columns per warpgroup: [0,64) operand A, [64,96) accumulator, [96,104) constant
+#define TC_WG_TMEM 96            // tensor-memory columns per warpgroup: [0,64) operand A, [64,96) accumulator
+#define TC_CONST_COL 480         // columns [480,488): the constant operand (1, 1, 0 ...) shared by all warpgroups
 #define TC_SPIN_LIMIT (1 << 20)
 #define TC_LBO 512               // bytes between 16-byte K chunks of operand B (32 rows x 16 bytes)
 #define TC_SBO 128               // bytes between groups of eight rows of operand B
@@ -171,12 +172,16 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
   const uint32_t t_wg = smem.tmem_base + wg * TC_WG_TMEM;               // lane 0 of this warpgroup's columns
   const uint32_t t_lane = t_wg + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes
   const uint32_t tA = t_lane, tD = t_lane + 64;
-  {  // columns [96,104): a constant operand (1, 1, 0 ...) that adds the second-layer bias as one more product
+  if (wg == 0) {  // the constant operand (1, 1, 0 ...) that adds the second-layer bias as one more product
     uint32_t one[8] = {0x3f800000u, 0x3f800000u, 0u, 0u, 0u, 0u, 0u, 0u};
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 ::"r"(t_lane + 96), "r"(one[0]), "r"(one[1]), "r"(one[2]), "r"(one[3]), "r"(one[4]), "r"(one[5]), "r"(one[6]), "r"(one[7]) : "memory");
+                 ::"r"(smem.tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + TC_CONST_COL), "r"(one[0]), "r"(one[1]), "r"(one[2]),
+                   "r"(one[3]), "r"(one[4]), "r"(one[5]), "r"(one[6]), "r"(one[7]) : "memory");
     tc_wait_st();
   }
+  tc_fence_before();
+  __syncthreads();  // every warpgroup's products may read the constant operand
+  tc_fence_after();
   constexpr uint64_t KSTEP = (2 * TC_LBO) >> 4;  // one product consumes two K chunks
   uint32_t parity = 0;
   bool timed_out = false;
@@ -351,7 +356,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
         tc_fence_after();
         const uint64_t desc_b2hi = tc_desc(smem_addr(sm.b2hi)), desc_b2lo = tc_desc(smem_addr(sm.b2lo));
         const uint64_t desc_b2bias = tc_desc(smem_addr(sm.b2bias));
-        tc_mma(t_wg + 64, t_wg + 96, desc_b2bias, TC_IDESC, 0);                                                    // bias
+        tc_mma(t_wg + 64, smem.tmem_base + TC_CONST_COL, desc_b2bias, TC_IDESC, 0);                                // bias
 #pragma unroll
         for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 32 + 8 * s, desc_b2hi + s * KSTEP, TC_IDESC, 1);      // lo x hi
 #pragma unroll

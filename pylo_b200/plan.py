@@ -263,11 +263,11 @@ class LoPlan:
                 continue
             X, Y = int(tdesc["X"][i]), int(tdesc["Y"][i])
             if self.tensor_cores:
-                # tensor-core kernel: an item is rt rows x 128 columns, taken by one warpgroup (4 per SM); rows per
+                # tensor-core kernel: an item is rt rows x 128 columns, taken by one warpgroup (5 per SM); rows per
                 # item as many as possible (the column terms are loaded once per item) while the tensor still yields
                 # >= 8 items per warpgroup
                 ncol = (Y + 127) // 128
-                rt = next((r for r in (64, 32, 16) if ((X + r - 1) // r) * ncol >= 8 * 592), 8)
+                rt = next((r for r in (64, 32, 16) if ((X + r - 1) // r) * ncol >= 8 * L.TC_WORKERS), 8)
                 width, tag = 128, rt
             elif family == L.FAM_ADAFAC:
                 cw = min((256, 128, 64, 32), key=lambda c: ((Y + c - 1) // c * c - Y, -c))
