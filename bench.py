@@ -38,7 +38,7 @@ B_BYTES = 40  # state_moments sweep: reads g, p, m(3), v; writes m(3), v
 # DRAM bytes per element (dram__bytes_read.sum + dram__bytes_write.sum) of each dominant kernel, from ncu
 # captures of a 4096 x 4096 case (profiles/*.md); traffic grows in proportion to the elements processed
 NCU_TRAFFIC_PER_ELEM = {("adafaclo", "apply_cols", "fp32"): 27.58, ("elo", "apply_cols", "fp32"): 27.58,
-                        ("adafaclo", "apply_cols", "3xtf32"): 27.52, ("elo", "apply_cols", "3xtf32"): 27.52}
+                        ("adafaclo", "apply_cols", "3xtf32"): 27.44, ("elo", "apply_cols", "3xtf32"): 27.44}
 # the tensor-core apply kernel issues 25 TF32 products of 128 x 32 x 8 per 128 parameters (two layers, three
 # products each for the high/low split, K padded to 32, one bias product)
 TC_ISSUED_FMA_PER_PARAM = 25 * 32 * 8
