@@ -335,19 +335,24 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
       parity ^= 1;
       tc_fence_after();
       // ---- hidden layer 1: relu, split, back into tensor memory as operand A of the second layer
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t dv[16], hi[16], lo[16];
-        tc_ld16(tD + 16 * half, dv);
+      {
+        uint32_t dv0[16], dv1[16];
+        tc_ld16(tD, dv0);       // both halves are requested before the first is touched: one load latency, not two
+        tc_ld16(tD + 16, dv1);
         tc_wait_ld();
+        auto split_store = [&](const uint32_t (&dv)[16], int half) {
+          uint32_t hi[16], lo[16];
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          const float h = fmaxf(__uint_as_float(dv[k]), 0.f), hh = tf32_hi(h);
-          hi[k] = __float_as_uint(hh);
-          lo[k] = __float_as_uint(h - hh);
-        }
-        tc_st16(tA + 16 * half, hi);
-        tc_st16(tA + 32 + 16 * half, lo);
+          for (int k = 0; k < 16; ++k) {
+            const float h = fmaxf(__uint_as_float(dv[k]), 0.f), hh = tf32_hi(h);
+            hi[k] = __float_as_uint(hh);
+            lo[k] = __float_as_uint(h - hh);
+          }
+          tc_st16(tA + 16 * half, hi);
+          tc_st16(tA + 32 + 16 * half, lo);
+        };
+        split_store(dv0, 0);
+        split_store(dv1, 1);
       }
       tc_wait_st();
       tc_fence_before();
@@ -371,18 +376,22 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
       tc_fence_after();
       // ---- hidden layer 2 (relu) and the two output heads as packed dot products over unit pairs
       uint64_t od[2] = {0ull, 0ull}, om[2] = {0ull, 0ull};
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t dv[16];
-        tc_ld16(tD + 16 * half, dv);
+      {
+        uint32_t dv0[16], dv1[16];
+        tc_ld16(tD, dv0);
+        tc_ld16(tD + 16, dv1);
         tc_wait_ld();
+        auto heads = [&](const uint32_t (&dv)[16], int half) {
 #pragma unroll
-        for (int jp = 0; jp < 8; ++jp) {
-          const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(&sm.w3[4 * (half * 8 + jp)]);  // (dir pair, mag pair)
-          const uint64_t r = pack2(fmaxf(__uint_as_float(dv[2 * jp]), 0.f), fmaxf(__uint_as_float(dv[2 * jp + 1]), 0.f));
-          od[jp & 1] = fma2(w.x, r, od[jp & 1]);
-          om[jp & 1] = fma2(w.y, r, om[jp & 1]);
-        }
+          for (int jp = 0; jp < 8; ++jp) {
+            const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(&sm.w3[4 * (half * 8 + jp)]);  // (dir pair, mag pair)
+            const uint64_t r = pack2(fmaxf(__uint_as_float(dv[2 * jp]), 0.f), fmaxf(__uint_as_float(dv[2 * jp + 1]), 0.f));
+            od[jp & 1] = fma2(w.x, r, od[jp & 1]);
+            om[jp & 1] = fma2(w.y, r, om[jp & 1]);
+          }
+        };
+        heads(dv0, 0);
+        heads(dv1, 1);
       }
       {
         float a, b, c, dd;
