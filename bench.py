@@ -38,10 +38,10 @@ B_BYTES = 40  # state_moments sweep: reads g, p, m(3), v; writes m(3), v
 # DRAM bytes per element (dram__bytes_read.sum + dram__bytes_write.sum) of each dominant kernel, from ncu
 # captures of a 4096 x 4096 case (profiles/*.md); traffic grows in proportion to the elements processed
 NCU_TRAFFIC_PER_ELEM = {("adafaclo", "apply_cols", "fp32"): 27.58, ("elo", "apply_cols", "fp32"): 27.58,
-                        ("adafaclo", "apply_cols", "3xtf32"): 27.44, ("elo", "apply_cols", "3xtf32"): 27.44}
+                        ("adafaclo", "apply_cols", "3xtf32"): 27.44, ("elo", "apply_cols", "3xtf32"): 27.44}  # none captured for 2xfp16
 # the tensor-core apply kernel issues 25 TF32 products of 128 x 32 x 8 per 128 parameters (two layers, three
 # products each for the high/low split, K padded to 32, one bias product)
-TC_ISSUED_FMA_PER_PARAM = 25 * 32 * 8
+TC_ISSUED_FMA_PER_PARAM = {"3xtf32": 25 * 32 * 8, "2xfp16": 13 * 32 * 16}
 
 
 def parse():
@@ -56,9 +56,9 @@ def parse():
     ap.add_argument("--no-orthogonalize", action="store_true", help="celo2 family: skip Newton-Schulz")
     ap.add_argument("--ns-precision", default="fp32", choices=["fp32", "3xtf32"],
                     help="celo2 family: Newton-Schulz products in fp32 (reference arithmetic) or as three TF32 tensor-core GEMMs")
-    ap.add_argument("--mlp-precision", default="3xtf32", choices=["fp32", "3xtf32"],
-                    help="adafaclo / elo: the network's hidden layers as scalar fp32 FMAs or as split-TF32 tensor-core "
-                         "products (fp32-faithful: three products per layer)")
+    ap.add_argument("--mlp-precision", default="3xtf32", choices=["fp32", "3xtf32", "2xfp16"],
+                    help="adafaclo / elo: the network's hidden layers as scalar fp32 FMAs, or as tensor-core products of "
+                         "operands split into two TF32 or two fp16 parts (fp32-faithful: three products per layer)")
     ap.add_argument("--blocks", type=int, default=8, help="N>1: stages whose parameter all-gathers overlap the next stage")
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "staged"],
                     help="N>1: how updated parameters reach the other ranks (peer stores fused into the apply kernels, "
@@ -458,11 +458,13 @@ def run_b200(args):
                      "achieved": owned_n * STEP_BYTES[args.optimizer] / (ms_per_step * 1e-3) / 1e9,
                      "frac": owned_n * STEP_BYTES[args.optimizer] / (ms_per_step * 1e-3) / 1e9 / peak},
         }
-        if args.optimizer in ("adafaclo", "elo") and dominant == "apply_cols" and args.mlp_precision == "3xtf32":
+        if args.optimizer in ("adafaclo", "elo") and dominant == "apply_cols" and args.mlp_precision in TC_ISSUED_FMA_PER_PARAM:
             # the tensor-core apply sweep is bound by the issue latency of its small (N = 32) products
-            issued = per_launch_elems * TC_ISSUED_FMA_PER_PARAM * 2 / (phase_ms[dominant] * 1e-3)
-            roofline["tensor"] = {"network_fma_per_param": 1600, "issued_tf32_fma_per_param": TC_ISSUED_FMA_PER_PARAM,
-                                  "issued_tf32_tflops": issued / 1e12,
+            per_param = TC_ISSUED_FMA_PER_PARAM[args.mlp_precision]
+            issued = per_launch_elems * per_param * 2 / (phase_ms[dominant] * 1e-3)
+            roofline["tensor"] = {"network_fma_per_param": 1600, "issued_fma_per_param": per_param,
+                                  "operands": "tf32" if args.mlp_precision == "3xtf32" else "fp16",
+                                  "issued_tflops": issued / 1e12,
                                   "network_fp32_equiv_tflops": per_launch_elems * 3200 / (phase_ms[dominant] * 1e-3) / 1e12}
         elif args.optimizer in ("adafaclo", "elo") and dominant in ("apply", "apply_cols") and clocks and clocks.get("sm_mhz"):
             # the apply sweep of the 39-32-32-2 network is bound by fp32 FMA issue, not by HBM

@@ -243,6 +243,14 @@ int pylo_b200_apply_adafac_cols(const pylo_tensor_desc* descs, const pylo_atile*
 int pylo_b200_apply_adafac_tc(const pylo_tensor_desc* descs, const pylo_atile* ttiles, int n_ttiles,
                               const pylo_step_params* prm, int* status, void* stream);
 
+/* The same with fp16 operands: every operand split into an fp16 high and an fp16 low part, products as
+ * kind::f16 (K = 16 per instruction, half the products and half the operand columns of the TF32 variant).  The
+ * features enter the products normalised (their rsqrt(mean f^2 + eps) is applied to the feature, not folded into
+ * the weights), which bounds them by sqrt(n) < 65504; conversions saturate.  Arguments as pylo_b200_apply_adafac_tc;
+ * one warpgroup of a CTA (six per SM) takes a whole item. */
+int pylo_b200_apply_adafac_tc16(const pylo_tensor_desc* descs, const pylo_atile* ttiles, int n_ttiles,
+                                const pylo_step_params* prm, int* status, void* stream);
+
 /* Phase C for the FAST2D tensors of the CELO2 and VELO families (same arithmetic as pylo_b200_apply, done on
  * pairs of adjacent elements with packed fp32x2 instructions).  ctiles: strip = row-tile index, cb = column-tile
  * index, pad_ = threads per row (8 .. 256, a thread owns 4 columns); a tile has 16 * (256 / pad_) rows and

@@ -95,6 +95,7 @@ def _load():
         "pylo_b200_apply": [vp, vp, i32, i32, C.POINTER(StepParams), vp],
         "pylo_b200_apply_adafac_cols": [vp, vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_apply_adafac_tc": [vp, vp, i32, C.POINTER(StepParams), vp, vp],
+        "pylo_b200_apply_adafac_tc16": [vp, vp, i32, C.POINTER(StepParams), vp, vp],
         "pylo_b200_apply_packed": [vp, vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_celo2_post_sums": [vp, vp, i32, vp],
         "pylo_b200_celo2_post_apply": [vp, vp, i32, vp],
@@ -117,7 +118,7 @@ def _load():
 lib, EXPORTED = _load()
 
 
-TC_WORKERS = 148 * 5  # warpgroups the tensor-core apply kernel runs at once (5 per SM)
+TC_WORKERS = {"tf32": 148 * 5, "fp16": 148 * 6}  # warpgroups a tensor-core apply kernel runs at once (5 or 6 per SM)
 STATIC_SCRATCH_TILES = 65536
 ERR_STATIC_SCRATCH_TOO_SMALL = -4
 

@@ -1035,6 +1035,7 @@ __global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const 
 }
 
 #include "pylo_apply_tc.cuh"
+#include "pylo_apply_tc16.cuh"
 
 // ================================================================================================
 // Phase C for CELO2 / ELO_CELO2 / VeLO on FAST2D tensors: packed kernel.
@@ -1566,6 +1567,21 @@ static int grid_for(int n_items, int ctas_per_sm) {
 }
 static int launch_status() { return (int)cudaGetLastError(); }
 
+// Opt a kernel in to more than 48 KB of dynamic shared memory, once per device (the attribute belongs to the
+// device's copy of the function); flags[] is the caller's per-kernel record.
+#define PYLO_MAX_DEVICES 64
+template <class K>
+static int allow_dynamic_smem(K kernel, int bytes, bool (&flags)[PYLO_MAX_DEVICES]) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev >= 0 && dev < PYLO_MAX_DEVICES && flags[dev]) return 0;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return (int)e;
+  if (dev >= 0 && dev < PYLO_MAX_DEVICES) flags[dev] = true;
+  return 0;
+}
+
 #define CHECK_ARG(cond) \
   do {                  \
     if (!(cond)) return -1; \
@@ -1721,12 +1737,8 @@ int pylo_b200_apply_adafac_cols(const pylo_tensor_desc* descs, const pylo_atile*
                                 const pylo_step_params* prm, void* stream) {
   CHECK_ARG(descs && ctiles && prm && n_ctiles >= 0 && prm->family == PYLO_FAM_ADAFAC);
   if (n_ctiles == 0) return 0;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(k_apply_adafac_cols, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(CcSmem));
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static bool configured[PYLO_MAX_DEVICES] = {};
+  if (int rc = allow_dynamic_smem(k_apply_adafac_cols, (int)sizeof(CcSmem), configured)) return rc;
   k_apply_adafac_cols<<<grid_for(n_ctiles, CC_CTAS_PER_SM), NT, sizeof(CcSmem), (cudaStream_t)stream>>>(descs, ctiles, n_ctiles, *prm);
   return launch_status();
 }
@@ -1737,13 +1749,20 @@ int pylo_b200_apply_adafac_tc(const pylo_tensor_desc* descs, const pylo_atile* t
   if (n_ttiles == 0) return 0;
   // more than half an SM's shared memory: one CTA per SM, which then owns all of the SM's tensor memory
   constexpr int smem = sizeof(TcSmem) > 120 * 1024 ? (int)sizeof(TcSmem) : 120 * 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(k_apply_adafac_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static bool configured[PYLO_MAX_DEVICES] = {};
+  if (int rc = allow_dynamic_smem(k_apply_adafac_tc, smem, configured)) return rc;
   k_apply_adafac_tc<<<grid_for(n_ttiles, 1), TC_NT, smem, (cudaStream_t)stream>>>(descs, ttiles, n_ttiles, *prm, status);
+  return launch_status();
+}
+
+int pylo_b200_apply_adafac_tc16(const pylo_tensor_desc* descs, const pylo_atile* ttiles, int n_ttiles,
+                                const pylo_step_params* prm, int* status, void* stream) {
+  CHECK_ARG(descs && ttiles && prm && n_ttiles >= 0 && prm->family == PYLO_FAM_ADAFAC);
+  if (n_ttiles == 0) return 0;
+  constexpr int smem = sizeof(ThSmem) > 120 * 1024 ? (int)sizeof(ThSmem) : 120 * 1024;  // one CTA per SM
+  static bool configured[PYLO_MAX_DEVICES] = {};
+  if (int rc = allow_dynamic_smem(k_apply_adafac_tc16, smem, configured)) return rc;
+  k_apply_adafac_tc16<<<grid_for(n_ttiles, 1), TH_NT, smem, (cudaStream_t)stream>>>(descs, ttiles, n_ttiles, *prm, status);
   return launch_status();
 }
 

@@ -124,9 +124,13 @@ class LoPlan:
 
     H = {L.FAM_ADAFAC: 32, L.FAM_CELO2: 8, L.FAM_VELO: 4}
 
-    def __init__(self, family: int, tensors: List[LoTensor], device, tensor_cores: bool = False):
+    def __init__(self, family: int, tensors: List[LoTensor], device, tensor_cores=False):
         self.family = family
-        self.tensor_cores = bool(tensor_cores) and family == L.FAM_ADAFAC
+        # False, or the operand format of the tensor-core apply kernel: "tf32" (True means this) or "fp16"
+        kind = "tf32" if tensor_cores is True else (tensor_cores or None)
+        if kind not in (None, "tf32", "fp16"):
+            raise ValueError(f"tensor_cores must be False, 'tf32' or 'fp16', got {tensor_cores!r}")
+        self.tensor_cores = kind if family == L.FAM_ADAFAC else None
         self.tensors = tensors
         self.device = torch.device(device)
         T = len(tensors)
@@ -263,11 +267,11 @@ class LoPlan:
                 continue
             X, Y = int(tdesc["X"][i]), int(tdesc["Y"][i])
             if self.tensor_cores:
-                # tensor-core kernel: an item is rt rows x 128 columns, taken by one warpgroup (5 per SM); rows per
+                # tensor-core kernel: an item is rt rows x 128 columns, taken by one warpgroup (5 or 6 per SM); rows per
                 # item as many as possible (the column terms are loaded once per item) while the tensor still yields
                 # >= 8 items per warpgroup
                 ncol = (Y + 127) // 128
-                rt = next((r for r in (64, 32, 16) if ((X + r - 1) // r) * ncol >= 8 * L.TC_WORKERS), 8)
+                rt = next((r for r in (64, 32, 16) if ((X + r - 1) // r) * ncol >= 8 * L.TC_WORKERS[self.tensor_cores]), 8)
                 width, tag = 128, rt
             elif family == L.FAM_ADAFAC:
                 cw = min((256, 128, 64, 32), key=lambda c: ((Y + c - 1) // c * c - Y, -c))
@@ -362,12 +366,12 @@ class LoPlan:
 
     def run_back(self, prm: L.StepParams, stream: int, reverse_c: bool = False):
         """Phases P, C."""
-        prm.no_tables = int(self.tensor_cores)
+        prm.no_tables = int(bool(self.tensor_cores))
         pp = C.byref(prm)
         self._call("prep_apply", L.lib.pylo_b200_prep_apply, self.desc.ptr, self.n_units, pp, stream)
         if self.n_ctiles and self.tensor_cores:
-            self._call("apply_cols", L.lib.pylo_b200_apply_adafac_tc, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp,
-                       self.status.data_ptr(), stream)
+            fn = L.lib.pylo_b200_apply_adafac_tc16 if self.tensor_cores == "fp16" else L.lib.pylo_b200_apply_adafac_tc
+            self._call("apply_cols", fn, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp, self.status.data_ptr(), stream)
         elif self.n_ctiles:
             fn = L.lib.pylo_b200_apply_adafac_cols if self.family == L.FAM_ADAFAC else L.lib.pylo_b200_apply_packed
             self._call("apply_cols", fn, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp, stream)

@@ -1,7 +1,8 @@
-"""GPU checks of the tensor-core variant of the AdafacLO / ELO apply kernel (``mlp_precision="3xtf32"``).
+"""GPU checks of the tensor-core variants of the AdafacLO / ELO apply kernel (``mlp_precision="3xtf32"`` and
+``"2xfp16"``).
 
-The two hidden layers run as tcgen05 TF32 products with every operand split into a high and a low part;
-the results must stay inside the same bounds as the scalar-FMA path: 1e-5 relative per element after one
+The two hidden layers run as tcgen05 products with every operand split into a high and a low part (TF32, or
+fp16 with normalised features); the results must stay inside the same bounds as the scalar-FMA path: 1e-5 relative per element after one
 step, 1e-4 after the whole trajectory, movement within 2e-3 of its largest entry against the oracle, and
 within 1e-5 of the movement against the scalar-FMA path of the library itself at the full 4096 x 4096 size.
 """
@@ -15,7 +16,7 @@ import golden_util as G
 
 pytestmark = pytest.mark.gpu
 
-TC = dict(mlp_precision="3xtf32")
+PRECISIONS = ["3xtf32", "2xfp16"]
 ADAFAC_CASES = sorted(n for n, c in G.CASES.items() if c["family"] in ("adafaclo", "elo"))
 
 
@@ -34,12 +35,13 @@ def _make(family, params, **kw):
     return optim.ELO_CUDA(params, lr=1e-2, weight_decay=0.1, clip_grad=True, network=_net(), **kw)
 
 
+@pytest.mark.parametrize("prec", PRECISIONS)
 @pytest.mark.parametrize("name", ADAFAC_CASES)
-def test_tensor_core_path_matches_oracle(name):
+def test_tensor_core_path_matches_oracle(name, prec):
     meta, weights, golden, _ = G.load(name)
     case = G.CASES[name]
     ref = G.run(case, G.make_oracle(case, weights, variant="cuda"))
-    got, opt, _ = CU.run_cuda(case, weights, **TC)
+    got, opt, _ = CU.run_cuda(case, weights, mlp_precision=prec)
     opt.check_status()
     assert any(plan.tensor_cores and plan.n_ctiles for _, plan in opt._plans.values()), "no tensor took the tensor-core kernel"
     res = CU.compare(got, ref, cases.init_values(case))
@@ -67,14 +69,15 @@ def test_scalar_fma_path_matches_oracle(name):
 TC_RAGGED = [(257, 129), (129, 300), (64, 128), (33, 37), (40, 4100), (7,), (5, 3)]
 
 
+@pytest.mark.parametrize("prec", PRECISIONS)
 @pytest.mark.parametrize("family", ["adafaclo", "elo"])
-def test_tensor_core_ragged_shapes_match_oracle(family):
+def test_tensor_core_ragged_shapes_match_oracle(family, prec):
     from oracle import pylo_oracle as O
 
     case = dict(name="tc_ragged", family=family, shapes=TC_RAGGED, net_seed=0, init_seed=5, init_scale=0.1, grad_seed=6,
                 grad_scale=0.3, steps=3, record=[1, 3], hparams={})
     params = [torch.nn.Parameter(v.cuda()) for v in cases.init_values(case)]
-    opt = _make(family, params, **TC)
+    opt = _make(family, params, mlp_precision=prec)
     kw = dict(lr=1e-2, elo=(family == "elo"))
     if family == "elo":
         kw.update(weight_decay=0.1, clip_grad=True)
@@ -92,26 +95,27 @@ def test_tensor_core_ragged_shapes_match_oracle(family):
     assert res[3][0] < 1e-5 and res[3][1] < 2e-3, res
 
 
+@pytest.mark.parametrize("prec", PRECISIONS)
 @pytest.mark.parametrize("family,extra", [("adafaclo", {}), ("adafaclo", {"weight_decay": 0.1}), ("elo", {})])
-def test_tensor_core_and_fma_paths_agree_at_full_size(family, extra):
+def test_tensor_core_and_fma_paths_agree_at_full_size(family, extra, prec):
     """4096 x 4096 and a 4096 x 1000 tensor (ragged last column block): the update through the tensor cores must
     equal the scalar-FMA one to 1e-5 of the largest movement (a few ulp of the parameter are discounted)."""
     shapes = [(4096, 4096), (4096, 1000)]
     outs, init = {}, None
-    for prec in ("fp32", "3xtf32"):
+    for which in ("fp32", prec):
         gen = torch.Generator(device="cuda").manual_seed(3)
         ps = [torch.nn.Parameter(torch.randn(*s, device="cuda", generator=gen) * 0.02) for s in shapes]
         init = [p.detach().clone() for p in ps]
         rows = [torch.exp(-7 + torch.randn(s[0], 1, device="cuda", generator=gen)) for s in shapes]
-        opt = _make(family, ps, mlp_precision=prec, **extra)
+        opt = _make(family, ps, mlp_precision=which, **extra)
         for t in (1, 2):
             g = torch.Generator(device="cuda").manual_seed(100 + t)
             for p, r in zip(ps, rows):
                 p.grad = torch.randn(*p.shape, device="cuda", generator=g) * r
             opt.step()
         opt.check_status()
-        outs[prec] = [p.detach().clone() for p in ps]
-    for a, b, w0 in zip(outs["fp32"], outs["3xtf32"], init):
+        outs[which] = [p.detach().clone() for p in ps]
+    for a, b, w0 in zip(outs["fp32"], outs[prec], init):
         moved = (a - w0).abs().max()
         assert moved > 0
         err = torch.clamp((a - b).abs() - 4 * 1.2e-7 * a.abs(), min=0).max()
@@ -119,12 +123,13 @@ def test_tensor_core_and_fma_paths_agree_at_full_size(family, extra):
         assert torch.allclose(a, b, rtol=1e-5, atol=1e-7)
 
 
-def test_tensor_core_path_is_bit_reproducible():
+@pytest.mark.parametrize("prec", PRECISIONS)
+def test_tensor_core_path_is_bit_reproducible(prec):
     outs = []
     for _ in range(2):
         gen = torch.Generator(device="cuda").manual_seed(3)
         p = torch.nn.Parameter(torch.randn(2048, 4096, device="cuda", generator=gen) * 0.02)
-        opt = _make("adafaclo", [p], **TC)
+        opt = _make("adafaclo", [p], mlp_precision=prec)
         for _ in range(2):
             p.grad = torch.randn(2048, 4096, device="cuda", generator=gen) * 1e-3
             opt.step()
