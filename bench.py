@@ -78,7 +78,7 @@ def workload_shapes(args):
 
 
 def grad_spec(args):
-    return {"llama3_8b": (1e-4, "iid"), "gpt2_medium": (1e-3, "outliers"), "vit_b16": (1e-3, "iid"),
+    return {"llama3_8b": (1e-4, "iid"), "llama3_block": (1e-4, "iid"), "gpt2_medium": (1e-3, "outliers"), "vit_b16": (1e-3, "iid"),
             "celo2_4096": (1.0, "rowlognormal"), "mlp_784": (1e-3, "iid")}[args.workload]
 
 

@@ -49,7 +49,13 @@ def llama3_8b(layers: int = 32) -> List[Shape]:
     return s
 
 
+def llama3_block() -> List[Shape]:
+    """One transformer block of Llama-3-8B (218 M params): a small multi-tensor case for kernel comparisons."""
+    return llama3_8b(1)[1:-2]
+
+
 WORKLOADS = {
+    "llama3_block": llama3_block,
     "mlp_784": mlp_784,
     "celo2_4096": celo2_4096,
     "vit_b16": vit_b16,
