@@ -254,7 +254,7 @@ def run_reference(args):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 def run_b200(args):
@@ -482,12 +482,27 @@ def run_b200(args):
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_of(args, shapes, world),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
+def emit(line):
+    """Print the result line on the real stdout (see main)."""
+    sys.stdout.flush()
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
+
+
+_REAL_STDOUT = 1
+
+
 def main():
+    # Libraries below (NCCL among them) sometimes write banners to file descriptor 1.  The contract is ONE JSON
+    # line on stdout, so descriptor 1 is pointed at stderr for the whole run and the line goes to a saved copy.
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     args = parse()
     if args.impl == "reference":
         run_reference(args)
