@@ -63,6 +63,8 @@ def parse():
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "staged"],
                     help="N>1: how updated parameters reach the other ranks (peer stores fused into the apply kernels, "
                          "or NCCL all-gathers per block)")
+    ap.add_argument("--no-multicast", action="store_true",
+                    help="N>1, fused exchange: one store per peer instead of one multimem store through the switch")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-steps", type=int, default=3)
@@ -291,7 +293,7 @@ def run_b200(args):
         # N>1: parameters reach the other ranks as peer stores from the apply kernels; N=1: plain flat buffer
         ok, why = 1, ""
         try:
-            shard = FusedShardedStep(shapes, dev, init_scale=0.02, seed=1)
+            shard = FusedShardedStep(shapes, dev, init_scale=0.02, seed=1, multicast=False if args.no_multicast else None)
         except Exception as e:  # symmetric memory unavailable on this box: fall back to NCCL gathers
             ok, why = 0, repr(e)
         if world > 1:
@@ -309,6 +311,8 @@ def run_b200(args):
         shard = ShardedStep.from_shapes(shapes, dev, init_scale=0.02, seed=1)
     else:                      # NCCL all-gathers per block, overlapped with the next block's kernels
         shard = StagedShardedStep(shapes, dev, blocks=min(args.blocks, 4), init_scale=0.02, seed=1)
+    if exchange == "fused" and getattr(shard, "multicast_base", 0):
+        exchange = "fused-multicast"
     args.exchange_used = exchange
     owned = shard.owned
     params = [shard.params[i] for i in owned]

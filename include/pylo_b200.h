@@ -89,7 +89,9 @@ typedef struct pylo_tensor_desc {
   const float* lr_mult; /* VeLO: device scalar multiplying lr for this tensor, else NULL */
   float* p_peer[PYLO_MAX_PEERS]; /* the same parameter inside the other ranks' peer-mapped buffers (first n_peer
                                     entries valid): kernels that write p store the new value there as well, which
-                                    replaces the all-gather of updated parameters */
+                                    replaces the all-gather of updated parameters.  n_peer < 0: p_peer[0] is a
+                                    multicast address mapping the parameter in every rank's buffer, and the kernels
+                                    issue one multimem store to it instead */
   int64_t n;        /* elements of this unit */
   int64_t m_stride; /* distance in floats between the three momentum planes (n for a whole tensor) */
   int64_t idx0;     /* offset of this unit's first element inside the [O,X,M,Y,I] view (0 for a whole tensor) */

@@ -663,16 +663,28 @@ __device__ __forceinline__ void network(const uint32_t s_w, float (&h1)[E][Fam<F
 // The parameter's copies in the other ranks' buffers (peer-mapped memory reached by plain stores).
 // The pointers are re-read from the descriptor at every store (they sit in L1) rather than held in
 // fourteen registers; with n_peer == 0 the cost is one compare.
+// n < 0: p[0] is a multicast address that maps every rank's buffer (NVLink switch multicast); one multimem
+// store then reaches all of them and the switch does the replication, so the writer's link carries each value
+// once instead of once per peer.
 struct Peers {
   float* const* p;
   int n;
 };
 __device__ __forceinline__ Peers load_peers(const pylo_tensor_desc& d) { return Peers{d.p_peer, d.n_peer}; }
 __device__ __forceinline__ void peer_store(const Peers& q, int64_t idx, float v) {
+  if (q.n < 0) {
+    asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(q.p[0] + idx), "f"(v) : "memory");
+    return;
+  }
 #pragma unroll 1
   for (int k = 0; k < q.n; ++k) q.p[k][idx] = v;
 }
 __device__ __forceinline__ void peer_store4(const Peers& q, int64_t idx, float4 v) {
+  if (q.n < 0) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(q.p[0] + idx), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+    return;
+  }
 #pragma unroll 1
   for (int k = 0; k < q.n; ++k) st4(q.p[k] + idx, v);
 }

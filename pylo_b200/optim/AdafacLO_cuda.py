@@ -106,7 +106,8 @@ class _AdafacFamily(Optimizer):
                 axis = dc - 1 if dc > dr else dc  # AdafacLO_cuda.py:342 (axis 0 is the decay axis)
             tensors.append(LoTensor(
                 p=p.data, m=st["exp_avg"], v=st["exp_avg_sq"], fac_r=st["exp_avg_sq_r"], fac_c=st["exp_avg_sq_c"],
-                fdims=fd, rcm_axis=axis, w=self._w_flat, peer_ptrs=getattr(p, "_pylo_peer_ptrs", None)))
+                fdims=fd, rcm_axis=axis, w=self._w_flat, peer_ptrs=getattr(p, "_pylo_peer_ptrs", None),
+                peer_multicast=getattr(p, "_pylo_peer_multicast", False)))
         return LoPlan(L.FAM_ADAFAC, tensors, self.device, tensor_cores={"fp32": False, "3xtf32": "tf32", "2xfp16": "fp16"}[self.mlp_precision])
 
     def check_status(self):

@@ -220,7 +220,8 @@ class VeLO_CUDA(Optimizer):
                 raise RuntimeError("VeLO_CUDA: every parameter needs a gradient on every step")
             fd = factored_dims_velo(tuple(p.shape))
             common = dict(p=p.data, m=st["mom"], v=st["rms"], fdims=fd, w=buf["weights"][li], lr_mult=buf["lr_mult"][li:li + 1],
-                          peer_ptrs=getattr(p, "_pylo_peer_ptrs", None))
+                          peer_ptrs=getattr(p, "_pylo_peer_ptrs", None),
+                peer_multicast=getattr(p, "_pylo_peer_multicast", False))
             if fd is not None:
                 tensors.append(LoTensor(fac_r=st["fac_vec_row"], fac_c=st["fac_vec_col"], rcm_axis=fd[0] + 1, **common))
             else:

@@ -47,6 +47,7 @@ class LoTensor:
     lr_mult: Optional[torch.Tensor] = None
     slice_last2: bool = False           # normalise features per matrix (last two axes) instead of per tensor
     peer_ptrs: Optional[Sequence[int]] = None  # device addresses of this parameter in the other ranks' buffers
+    peer_multicast: bool = False  # peer_ptrs holds ONE multicast address that maps the parameter on every rank
 
 
 def geometry(shape: Sequence[int], fdims):
@@ -159,7 +160,7 @@ class LoPlan:
                 if len(t.peer_ptrs) > L.MAX_PEERS:
                     raise ValueError(f"at most {L.MAX_PEERS} peers (8 GPUs of one box)")
                 d["p_peer"][: len(t.peer_ptrs)] = list(t.peer_ptrs)
-                d["n_peer"] = len(t.peer_ptrs)
+                d["n_peer"] = -1 if t.peer_multicast else len(t.peer_ptrs)
             if t.fdims is None:
                 d["mode"] = L.MODE_VEC1D
                 d["O"] = d["X"] = d["M"] = d["I"] = 1

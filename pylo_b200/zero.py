@@ -188,7 +188,10 @@ class FusedShardedStep:
     """
 
     def __init__(self, shapes: Sequence[Tuple[int, ...]], device, init_scale: float = 0.02, seed: int = 1,
-                 process_group=None, cost=None):
+                 process_group=None, cost=None, multicast: Optional[bool] = None):
+        """``multicast``: reach the peers through the NVLink switch's multicast mapping of the buffer (one
+        ``multimem`` store per value, replicated by the switch) instead of one store per peer.  None: use it
+        where the symmetric memory offers a multicast address, True: require it, False: never."""
         self.pg = process_group
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
@@ -204,9 +207,14 @@ class FusedShardedStep:
             bases = [int(b) for b in self.handle.buffer_ptrs]
             if bases[self.rank] != self.flat.data_ptr():
                 raise RuntimeError("symmetric memory rendezvous returned an unexpected local address")
+            mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+            if multicast and not mc:
+                raise RuntimeError("multicast=True, but the symmetric memory has no multicast address on this system")
+            self.multicast_base = mc if multicast is not False else 0
         else:
             self.flat = torch.zeros(n, dtype=torch.float32, device=device)
             bases = [self.flat.data_ptr()]
+            self.multicast_base = 0
         gen = torch.Generator(device=device)
         self.params = []
         for i, (off, s) in enumerate(zip(self.offsets, shapes)):
@@ -216,7 +224,11 @@ class FusedShardedStep:
             self.params.append(torch.nn.Parameter(view, requires_grad=True))
         self.owned = [i for i, r in enumerate(self.owner) if r == self.rank]
         for i in self.owned:  # where this tensor lives in every other rank's buffer
-            self.params[i]._pylo_peer_ptrs = [bases[r] + 4 * self.offsets[i] for r in range(self.world) if r != self.rank]
+            if self.multicast_base:
+                self.params[i]._pylo_peer_ptrs = [self.multicast_base + 4 * self.offsets[i]]
+                self.params[i]._pylo_peer_multicast = True
+            else:
+                self.params[i]._pylo_peer_ptrs = [bases[r] + 4 * self.offsets[i] for r in range(self.world) if r != self.rank]
         self._token = torch.zeros(1, dtype=torch.float32, device=device)
 
     def param_groups(self, is_embedding=None, groups: int = 1):

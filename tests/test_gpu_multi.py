@@ -127,7 +127,7 @@ def _staged_worker(rank, world, port, out):
         dist.destroy_process_group()
 
 
-def _fused_worker(rank, world, port, family, out):
+def _fused_worker(rank, world, port, family, out, multicast=False):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
@@ -139,7 +139,10 @@ def _fused_worker(rank, world, port, family, out):
 
         shapes = SHAPES + [(72, 48), (300, 260)]
         case = dict(CASE, shapes=shapes)
-        shard = FusedShardedStep(shapes, dev, init_scale=0.05, seed=4)
+        shard = FusedShardedStep(shapes, dev, init_scale=0.05, seed=4, multicast=multicast)
+        if multicast is None and not shard.multicast_base:
+            out.put((rank, "no-multicast"))
+            return
         start = [p.detach().clone() for p in shard.params]
         loss = lambda t: torch.tensor(cases.velo_loss(t), device=dev)
 
@@ -208,6 +211,25 @@ def test_two_rank_fused_exchange_is_bit_identical(family):
     results = [out.get(timeout=300) for _ in procs]
     for p in procs:
         p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results
+
+
+@pytest.mark.parametrize("family", ["adafaclo", "velo"])
+def test_two_rank_fused_multicast_exchange_is_bit_identical(family):
+    """The same through the NVLink switch's multicast mapping of the buffer: one multimem store per value."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_fused_worker, args=(r, 2, port, family, out, None)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    if any(msg == "no-multicast" for _, msg in results):
+        pytest.skip("the symmetric memory offers no multicast address on this system")
     assert all(msg == "ok" for _, msg in results), results
 
 
