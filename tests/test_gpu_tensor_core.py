@@ -66,7 +66,7 @@ def test_scalar_fma_path_matches_oracle(name):
 
 # two-dimensional shapes that are factored (both sides >= 32) with ragged edges: columns that do not fill a
 # block of 128, fewer rows than one work item, a single block; plus tensors that stay on the generic kernel
-TC_RAGGED = [(257, 129), (129, 300), (64, 128), (33, 37), (40, 4100), (7,), (5, 3)]
+TC_RAGGED = [(257, 129), (129, 300), (64, 128), (33, 37), (40, 4100), (300, 1000), (7,), (5, 3)]
 
 
 @pytest.mark.parametrize("prec", PRECISIONS)
