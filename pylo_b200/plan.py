@@ -291,6 +291,9 @@ class LoPlan:
         self.n_ctiles = len(ctiles)
         #: device flag the tensor-core kernel raises when one of its bounded waits ran out
         self.status = torch.zeros(64, dtype=torch.int32, device=self.device) if self.tensor_cores else None
+        # a pinned copy of the flag follows every launch without blocking; the next launch looks at it once it landed
+        self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory() if self.tensor_cores else None
+        self._status_event = None
         fast_unit = udesc["mode"] == L.MODE_FAST2D
         slow = tiles[~fast_unit[tiles["tensor"]]] if len(tiles) else tiles
         self.tiles_slow = DeviceTable(np.ascontiguousarray(slow), self.device)
@@ -371,8 +374,15 @@ class LoPlan:
         pp = C.byref(prm)
         self._call("prep_apply", L.lib.pylo_b200_prep_apply, self.desc.ptr, self.n_units, pp, stream)
         if self.n_ctiles and self.tensor_cores:
+            if self._status_event is not None and self._status_event.query() and int(self._status_host[0]) != 0:
+                raise L.PyloLibError("apply_adafac_tc: a wait on the tensor core timed out in an earlier step; "
+                                     "the parameters written since are invalid")
             fn = L.lib.pylo_b200_apply_adafac_tc16 if self.tensor_cores == "fp16" else L.lib.pylo_b200_apply_adafac_tc
             self._call("apply_cols", fn, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp, self.status.data_ptr(), stream)
+            if stream == current_stream_ptr():  # the watch copy is enqueued by torch on its current stream
+                self._status_host.copy_(self.status[:1], non_blocking=True)
+                self._status_event = torch.cuda.Event()
+                self._status_event.record()
         elif self.n_ctiles:
             fn = L.lib.pylo_b200_apply_adafac_cols if self.family == L.FAM_ADAFAC else L.lib.pylo_b200_apply_packed
             self._call("apply_cols", fn, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp, stream)

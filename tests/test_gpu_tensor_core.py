@@ -142,3 +142,24 @@ def test_unknown_mlp_precision_is_rejected():
     p = torch.nn.Parameter(torch.zeros(64, 64, device="cuda"))
     with pytest.raises(ValueError):
         _make("adafaclo", [p], mlp_precision="bf16")
+
+
+def test_timed_out_wait_is_reported_by_a_later_step():
+    """The kernel ORs 1 into a device flag when one of its bounded waits runs out.  Here the flag is set from the
+    host (no GPU misbehaviour involved): check_status() must raise, and so must a later step on its own."""
+    from pylo_b200 import _lib as L
+
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    p = torch.nn.Parameter(torch.randn(256, 256, device="cuda", generator=gen) * 0.02)
+    opt = _make("adafaclo", [p], mlp_precision="3xtf32")
+    p.grad = torch.randn(256, 256, device="cuda", generator=gen) * 1e-3
+    opt.step()
+    opt.check_status()
+    plan = list(opt._plans.values())[0][1]
+    plan.status[0] = 1
+    with pytest.raises(L.PyloLibError):
+        opt.check_status()
+    opt.step()                 # this launch is followed by a copy of the flag to pinned memory
+    torch.cuda.synchronize()
+    with pytest.raises(L.PyloLibError):
+        opt.step()             # ... which the next launch looks at
