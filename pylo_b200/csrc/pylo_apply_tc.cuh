@@ -32,6 +32,9 @@
 #define TC_WG_TMEM 96            // tensor-memory columns per warpgroup: [0,64) operand A, [64,96) accumulator
 #define TC_CONST_COL 480         // columns [480,488): the constant operand (1, 1, 0 ...) shared by all warpgroups
 #define TC_SPIN_LIMIT (1 << 20)
+#ifndef TC_POLL_SLEEP_NS
+#define TC_POLL_SLEEP_NS 40
+#endif
 #define TC_LBO 512               // bytes between 16-byte K chunks of operand B (32 rows x 16 bytes)
 #define TC_SBO 128               // bytes between groups of eight rows of operand B
 
@@ -70,6 +73,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(a), "r"(parity) : "memory");
     if (ok) return true;
+    __nanosleep(TC_POLL_SLEEP_NS);  // back off: a waiting warp should not spend the issue slots of the working ones
   }
   return false;
 }
@@ -251,6 +255,8 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
     wg_barrier(wg);
     const float fb0 = d.f_b[yc], fb1 = d.f_b[Y + yc], fb2 = d.f_b[2 * (int64_t)Y + yc];
     const volatile TcItem& ic = sm.item;
+    // no clipping, no nan_to_num, no global-norm scale (AdafacLO's defaults): the gradient is used as it is
+    const bool plain_grad = !prm.nan_to_num && prm.clip_val == CUDART_INF_F && ic.gs == 1.0f;
     float cg, cp, cm0, cm1, cm2, cv;
     auto load_row = [&](int x, float& g, float& p, float& m0, float& m1, float& m2, float& v) {
       const int64_t idx = (colok && x < X) ? (int64_t)x * Y + y : 0;
@@ -283,7 +289,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
       fac_next = load_fac(x + 2);
       // ---- operand A of the first layer, high and low parts
       {
-        const float g = xform_grad(cg, ic.gs, prm.clip_val, prm.nan_to_num);
+        const float g = plain_grad ? cg : xform_grad(cg, ic.gs, prm.clip_val, prm.nan_to_num);
         const float rs = rsqrt_pos(cv + prm.eps_feat);
         const float4 cfa = sm.rowf[i & 1][3];
         const float k0 = cfa.x * fb0, k1 = cfa.y * fb1, k2 = cfa.z * fb2;
