@@ -181,6 +181,8 @@ __global__ void __launch_bounds__(TH_NT, 1) k_apply_adafac_tc16(const pylo_tenso
     // column factors of the element-wise factored features, with those features' normalisers folded in
     const float fb0 = d.f_b[yc], fb1 = d.f_b[Y + yc], fb2 = d.f_b[2 * (int64_t)Y + yc];
     const volatile TcItem& ic = sm.item;
+    // no clipping, no nan_to_num, no global-norm scale (AdafacLO's defaults): the gradient is used as it is
+    const bool plain_grad = !prm.nan_to_num && prm.clip_val == CUDART_INF_F && ic.gs == 1.0f;
     float cg, cp, cm0, cm1, cm2, cv;
     auto load_row = [&](int x, float& g, float& p, float& m0, float& m1, float& m2, float& v) {
       const int64_t idx = (colok && x < X) ? (int64_t)x * Y + y : 0;
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__(TH_NT, 1) k_apply_adafac_tc16(const pylo_tenso
       load_next(x + 2);
       // ---- operand A of the first layer: normalised features, high and low halves
       {
-        const float g = xform_grad(cg, ic.gs, prm.clip_val, prm.nan_to_num);
+        const float g = plain_grad ? cg : xform_grad(cg, ic.gs, prm.clip_val, prm.nan_to_num);
         const float rs = rsqrt_pos(cv + prm.eps_feat);
         const uint4 rw0 = sm.rowf[i & 1][0], rw1 = sm.rowf[i & 1][1], rw2 = sm.rowf[i & 1][2];
         const float k0 = __uint_as_float(rw1.z) * fb0, k1 = __uint_as_float(rw1.w) * fb1, k2 = __uint_as_float(rw2.x) * fb2;
