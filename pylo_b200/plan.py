@@ -115,6 +115,29 @@ class DeviceTable:
         self._events[i] = ev
 
 
+def apply_tile_shape(family: int, X: int, Y: int, tensor_cores=None):
+    """(rows per work item, columns per work item, tag for ``pylo_atile.pad_``) of a FAST2D tensor's apply sweep.
+
+    * tensor-core kernels (AdafacLO family, ``tensor_cores`` = "tf32" / "fp16"): an item is rt rows x 128 columns,
+      taken by one warpgroup (5 or 6 per SM); as many rows as possible (the column terms are loaded once per item)
+      while the tensor still yields >= 8 items per warpgroup; tag = rt;
+    * AdafacLO family on the CUDA cores: n_sub sub-tiles of 32 rows in one block of 32..256 columns, as long as
+      possible while the tensor still yields >= 8 items per SM; tag = columns | n_sub << 16;
+    * CELO2 / VeLO: four columns per thread, tag = threads per row.
+    """
+    if tensor_cores:
+        ncol = (Y + 127) // 128
+        rt = next((r for r in (64, 32, 16) if ((X + r - 1) // r) * ncol >= 8 * L.TC_WORKERS[tensor_cores]), 8)
+        return rt, 128, rt
+    if family == L.FAM_ADAFAC:
+        cw = min((256, 128, 64, 32), key=lambda c: ((Y + c - 1) // c * c - Y, -c))
+        ncol = (Y + cw - 1) // cw
+        n_sub = next((k for k in (8, 4, 2) if ((X + 32 * k - 1) // (32 * k)) * ncol >= 1184), 1)
+        return 32 * n_sub, cw, cw | (n_sub << 16)
+    tpr = min((256, 128, 64, 32, 16, 8), key=lambda c: ((Y + 4 * c - 1) // (4 * c) * 4 * c - Y, -c))
+    return 16 * (256 // tpr), 4 * tpr, tpr
+
+
 class LoPlan:
     """Descriptor tables, tile lists and workspace for the tensors of one optimizer instance.
 
@@ -259,31 +282,14 @@ class LoPlan:
         self.n_units = U
         self.total_elems = int(sum(sizes))
         self._keepalive = []
-        # FAST2D tensors take a column-owning apply kernel (AdafacLO/ELO: one column per thread, 16 or 32 rows;
-        # CELO2/VeLO: four columns per thread, 8 rows per thread); everything else the generic one
+        # FAST2D tensors take a tiled apply kernel (see apply_tile_shape); everything else the generic one
         ctiles = []
         unit_of = {i: u for u, (i, _) in enumerate(unit_owner)}  # a FAST2D tensor is never sliced: one unit
         for i in range(T):
             if tdesc["mode"][i] != L.MODE_FAST2D:
                 continue
             X, Y = int(tdesc["X"][i]), int(tdesc["Y"][i])
-            if self.tensor_cores:
-                # tensor-core kernel: an item is rt rows x 128 columns, taken by one warpgroup (5 or 6 per SM); rows per
-                # item as many as possible (the column terms are loaded once per item) while the tensor still yields
-                # >= 8 items per warpgroup
-                ncol = (Y + 127) // 128
-                rt = next((r for r in (64, 32, 16) if ((X + r - 1) // r) * ncol >= 8 * L.TC_WORKERS[self.tensor_cores]), 8)
-                width, tag = 128, rt
-            elif family == L.FAM_ADAFAC:
-                cw = min((256, 128, 64, 32), key=lambda c: ((Y + c - 1) // c * c - Y, -c))
-                ncol = (Y + cw - 1) // cw
-                # a work item is n_sub sub-tiles of 32 rows in one column block (the column terms are loaded
-                # once per item); as long as possible while the tensor still yields >= 8 items per SM
-                n_sub = next((k for k in (8, 4, 2) if ((X + 32 * k - 1) // (32 * k)) * ncol >= 1184), 1)
-                rt, width, tag = 32 * n_sub, cw, cw | (n_sub << 16)
-            else:
-                tpr = min((256, 128, 64, 32, 16, 8), key=lambda c: ((Y + 4 * c - 1) // (4 * c) * 4 * c - Y, -c))
-                rt, width, tag = 16 * (256 // tpr), 4 * tpr, tpr
+            rt, width, tag = apply_tile_shape(family, X, Y, self.tensor_cores)
             for rtile in range((X + rt - 1) // rt):
                 for ctile in range((Y + width - 1) // width):
                     ctiles.append((unit_of[i], rtile, ctile, tag))

@@ -107,3 +107,26 @@ def test_cuda_classes_refuse_to_run_without_a_gpu():
         optim.CELO2_CUDA(p, network=models.CELO2MLP())
     with pytest.raises(RuntimeError):
         optim.AdafacLO_CUDA(p, network=models.MetaMLP(39, 32, 1))
+
+
+@pytest.mark.parametrize("tc", [None, "tf32", "fp16"])
+@pytest.mark.parametrize("family", [L.FAM_ADAFAC, L.FAM_CELO2])
+@pytest.mark.parametrize("X,Y", [(4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096), (40, 4100), (129, 300), (64, 128)])
+def test_apply_items_cover_a_tensor_exactly_once(family, X, Y, tc):
+    """Work items of the tiled apply sweeps: whole rows x column blocks, every element in exactly one item."""
+    if tc and family != L.FAM_ADAFAC:
+        pytest.skip("tensor-core kernels exist for the AdafacLO family only")
+    rt, width, tag = plan.apply_tile_shape(family, X, Y, tc)
+    n_r, n_c = (X + rt - 1) // rt, (Y + width - 1) // width
+    assert (n_r - 1) * rt < X <= n_r * rt and (n_c - 1) * width < Y <= n_c * width
+    if tc:
+        assert width == 128 and tag == rt and rt in (8, 16, 32, 64)
+        # as many rows per item as leave every warpgroup at least eight items, never below eight rows
+        workers = L.TC_WORKERS[tc]
+        assert rt == 8 or n_r * n_c >= 8 * workers
+        if rt < 64:
+            assert ((X + 2 * rt - 1) // (2 * rt)) * n_c < 8 * workers
+    elif family == L.FAM_ADAFAC:
+        assert width in (32, 64, 128, 256) and tag & 0xffff == width and rt == 32 * (tag >> 16)
+    else:
+        assert width == 4 * tag and rt == 16 * (256 // tag)
