@@ -5,23 +5,33 @@
                     [--workload llama3_8b|gpt2_medium|vit_b16|celo2_4096|mlp_784] [--optimizer adafaclo|...]
 
 One "step" is one ``optimizer.step()`` over every parameter tensor of the
-workload (plus, with more than one GPU, the all-gather of the updated
+workload (plus, with more than one GPU, the exchange of the updated
 parameters).  Tensors are owned ZeRO-1 style by one rank each, so the total
 work is fixed as N grows (strong scaling).  Prints ONE JSON line on rank 0.
 
+The headline line is AdafacLO over the Llama-3-8B parameter shapes.  With the
+default workload the line also carries ``extra_configs``: the other benchmark
+configurations (VeLO over the GPT-2-medium shapes, CELO2 on one 4096 x 4096
+weight, ELO_CELO2 over the ViT-B/16 shapes, CELO2 over the Llama shapes), each
+with Newton-Schulz off and on where the family has it, measured after the
+headline in the same process.
+
 ``--impl reference`` times the CPU restatement of the reference's step
 (oracle/pylo_oracle.py) on the host cores of the box, on a bounded sample of the
-same workload; it is the only place besides the ``cpu_baseline`` leg where this
-script executes anything under oracle/.
+same workload; it is the only place besides the ``cpu_baseline`` and
+``reference_cuda`` legs where this script executes anything under oracle/, and
+it does not load the CUDA library of this package.
 """
 
 import argparse
+import copy
 import json
 import os
 import subprocess
 import sys
 import threading
 import time
+import types
 
 import torch
 
@@ -35,16 +45,14 @@ STEP_BYTES = {"adafaclo": 44, "elo": 44, "velo": 44, "celo2": 56, "elo_celo2": 5
 # compulsory bytes per parameter of the apply sweep alone (reads g, p, m(3), v; writes p or the raw step)
 APPLY_BYTES = 28
 B_BYTES = 40  # state_moments sweep: reads g, p, m(3), v; writes m(3), v
-# DRAM bytes per element (dram__bytes_read.sum + dram__bytes_write.sum) of each dominant kernel, from ncu
-# captures of a 4096 x 4096 case (profiles/*.md); traffic grows in proportion to the elements processed
-NCU_TRAFFIC_PER_ELEM = {("adafaclo", "apply_cols", "fp32"): 27.58, ("elo", "apply_cols", "fp32"): 27.58,
-                        ("adafaclo", "apply_cols", "3xtf32"): 27.44, ("elo", "apply_cols", "3xtf32"): 27.44}  # none captured for 2xfp16
-# the tensor-core apply kernel issues 25 TF32 products of 128 x 32 x 8 per 128 parameters (two layers, three
-# products each for the high/low split, K padded to 32, one bias product)
+# DRAM bytes per element (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels: CONSTANTS taken
+# from ncu captures of a 4096 x 4096 case, not measured in this run; traffic grows in proportion to the elements
+NCU_TRAFFIC_PER_ELEM = {"k_apply_adafac_cols": 27.58, "k_apply_adafac_tc": 27.44}
+# TF32 / fp16 multiply-adds the tensor-core apply kernels issue per parameter (products x N x K, M = the element)
 TC_ISSUED_FMA_PER_PARAM = {"3xtf32": 25 * 32 * 8, "2xfp16": 13 * 32 * 16}
 
 
-def parse():
+def parse(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
@@ -67,8 +75,20 @@ def parse():
                     help="N>1, fused exchange: one store per peer instead of one multimem store through the switch")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the other benchmark configurations (extra_configs)")
+    ap.add_argument("--no-reference-cuda", action="store_true", help="skip the timing of the reference's own CUDA kernels")
     ap.add_argument("--cpu-sample-steps", type=int, default=3)
-    return ap.parse_args()
+    return ap.parse_args(argv)
+
+
+def import_without_native_library():
+    """Make ``pylo_b200.workloads`` and ``pylo_b200.models`` importable WITHOUT running the package's
+    ``__init__`` (which loads libpylo_b200.so): the CPU reference arm needs only shape lists and the seeded
+    meta-networks, and must not map this package's CUDA library into its process."""
+    if "pylo_b200" not in sys.modules:
+        pkg = types.ModuleType("pylo_b200")
+        pkg.__path__ = [os.path.join(ROOT, "pylo_b200")]
+        sys.modules["pylo_b200"] = pkg
 
 
 def workload_shapes(args):
@@ -245,6 +265,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    import_without_native_library()
     shapes = workload_shapes(args)
     steps = max(1, args.steps)
     value, cores, desc, mean = run_cpu_oracle(args, shapes, steps, warmup=max(1, min(args.warmup, 2)))
@@ -259,19 +280,27 @@ def run_reference(args):
     emit(line)
 
 
-def run_b200(args):
+def replica_checksum(flat):
+    """Order-independent, exact checksums of a rank's whole flat parameter buffer: the sum of its bit patterns
+    (as integers) and the sum of their squares modulo 2^63, taken in chunks so that nothing large is allocated."""
+    s1 = torch.zeros((), dtype=torch.int64, device=flat.device)
+    s2 = torch.zeros((), dtype=torch.int64, device=flat.device)
+    bits = flat.view(torch.int32)
+    step = 1 << 26
+    for lo in range(0, bits.numel(), step):
+        c = bits[lo:lo + step].to(torch.int64)
+        s1 += c.sum()
+        s2 += (c * c).remainder(2147483647).sum()
+    return torch.stack([s1, s2])
+
+
+def measure(args, dev, world, rank, local, headline):
+    """One configuration on the current process group: returns the JSON line (rank 0) or None."""
     import torch.distributed as dist
 
     from pylo_b200 import workloads as W
     from pylo_b200.zero import FusedShardedStep, ShardedStep, StagedShardedStep
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     shapes = workload_shapes(args)
     total = W.total_params(shapes)
     gscale, gkind = grad_spec(args)
@@ -281,7 +310,7 @@ def run_b200(args):
     state_bytes = 16 if args.optimizer not in ("celo2", "elo_celo2") else 20
     need = total * 4 + (total / world) * (state_bytes + 1) * 1.02 + 4e9
     if need > free * 0.97:
-        raise SystemExit(f"workload needs ~{need / 1e9:.0f} GB per GPU, {free / 1e9:.0f} GB free: refusing to run")
+        raise MemoryError(f"workload needs ~{need / 1e9:.0f} GB per GPU, {free / 1e9:.0f} GB free: refusing to run")
 
     exchange = args.exchange
     if exchange == "auto":
@@ -357,6 +386,7 @@ def run_b200(args):
     for pl in plans():
         pl.enable_profile(True)
         pl.launch_count = 0
+    extra_launches0 = getattr(opt, "extra_launches", 0)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -372,10 +402,10 @@ def run_b200(args):
         opt.check_status()  # raises if a bounded wait of the tensor-core kernel ran out during the timed steps
     clocks = sampler.stop() if rank == 0 else None
     phase = {}
-    launches = 0
+    launches = getattr(opt, "extra_launches", 0) - extra_launches0
     for pl in plans():
         for k, v in pl.phase_times().items():
-            phase.setdefault(k, []).extend(v)
+            phase.setdefault(pl.KERNEL_OF.get(k, k), []).extend(v)
         launches += pl.launch_count
         pl.enable_profile(False)
     t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
@@ -386,7 +416,7 @@ def run_b200(args):
 
     # ---- end to end: gradients arrive from pinned host memory, a probe of the result goes back
     e2e = None
-    if not args.no_e2e:
+    if headline and not args.no_e2e:
         pinned = {s: torch.empty(s, dtype=torch.float32).pin_memory() for s in pool}
         for s, buf in pinned.items():
             buf.copy_(pool[s])
@@ -432,7 +462,20 @@ def run_b200(args):
             dist.all_reduce(hb)
         e2e = {"value": total / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": int(hb[0].item()), "d2h_bytes_per_step": int(hb[1].item())}
+        opt.before_group = None
 
+    # ---- every rank must now hold the same parameters, bit for bit
+    replica = None
+    if world > 1:
+        barrier()
+        mine = replica_checksum(shard.flat)
+        allsums = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allsums, mine)
+        replica = {"ranks": world, "equal": bool(all(torch.equal(a, allsums[0]) for a in allsums)),
+                   "what": "sum of bit patterns and sum of their squares (mod 2^31-1) of every rank's whole flat "
+                           "parameter buffer after the last step"}
+
+    line = None
     if rank == 0:
         peaks = {}
         try:
@@ -448,47 +491,136 @@ def run_b200(args):
         lo_elems = sum(pl.total_elems for pl in plans())
         n_launch = max(len(phase.get(dominant, [])), 1)
         per_launch_elems = lo_elems * args.steps / n_launch if dominant else 0
-        kbytes = {"apply": APPLY_BYTES, "apply_cols": APPLY_BYTES, "state_moments": B_BYTES, "rowcol_sums": 4}.get(dominant, 0)
+        kbytes = B_BYTES if dominant == "k_state_moments" else (4 if dominant == "k_rowcol_fast" else
+                                                                 (APPLY_BYTES if dominant and dominant.startswith("k_apply") else 0))
         achieved = per_launch_elems * kbytes / (phase_ms.get(dominant, 1e9) * 1e-3) / 1e9 if dominant else 0.0
         roofline = {
             "bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
             "frac": achieved / peak, "peak_source": f"{peak_src} (MEASURED_PEAKS.json hbm_gbs)",
-            "traffic": (NCU_TRAFFIC_PER_ELEM[(args.optimizer, dominant, args.mlp_precision)] * per_launch_elems
-                        if (args.optimizer, dominant, args.mlp_precision) in NCU_TRAFFIC_PER_ELEM else None),
-            "traffic_note": "ncu dram bytes per element of a 4096x4096 capture x elements per launch",
+            "traffic": (NCU_TRAFFIC_PER_ELEM[dominant] * per_launch_elems if dominant in NCU_TRAFFIC_PER_ELEM else None),
+            "traffic_note": "constant: dram bytes per element from an ncu capture of a 4096x4096 case, times the elements "
+                            "of one launch (not measured in this run)",
             "algorithmic_bytes_per_param": kbytes, "avg_launch_ms": phase_ms.get(dominant),
-            "phase_ms_per_launch": phase_ms,
+            "phase_ms_per_launch": phase_ms, "phase_share": {k: v / max(sum(phase_share.values()), 1e-9) for k, v in phase_share.items()},
             "step": {"algorithmic_bytes_per_param": STEP_BYTES[args.optimizer],
                      "achieved": owned_n * STEP_BYTES[args.optimizer] / (ms_per_step * 1e-3) / 1e9,
                      "frac": owned_n * STEP_BYTES[args.optimizer] / (ms_per_step * 1e-3) / 1e9 / peak},
         }
-        if args.optimizer in ("adafaclo", "elo") and dominant == "apply_cols" and args.mlp_precision in TC_ISSUED_FMA_PER_PARAM:
-            # the tensor-core apply sweep is bound by the issue latency of its small (N = 32) products
+        if args.optimizer in ("adafaclo", "elo") and dominant in ("k_apply_adafac_tc", "k_apply_adafac_tc16"):
             per_param = TC_ISSUED_FMA_PER_PARAM[args.mlp_precision]
             issued = per_launch_elems * per_param * 2 / (phase_ms[dominant] * 1e-3)
             roofline["tensor"] = {"network_fma_per_param": 1600, "issued_fma_per_param": per_param,
                                   "operands": "tf32" if args.mlp_precision == "3xtf32" else "fp16",
                                   "issued_tflops": issued / 1e12,
                                   "network_fp32_equiv_tflops": per_launch_elems * 3200 / (phase_ms[dominant] * 1e-3) / 1e12}
-        elif args.optimizer in ("adafaclo", "elo") and dominant in ("apply", "apply_cols") and clocks and clocks.get("sm_mhz"):
+        elif args.optimizer in ("adafaclo", "elo") and dominant in ("k_apply", "k_apply_adafac_cols") and clocks and clocks.get("sm_mhz"):
             # the apply sweep of the 39-32-32-2 network is bound by fp32 FMA issue, not by HBM
             fma = per_launch_elems * 1600 / (phase_ms[dominant] * 1e-3)
             peak_fma = 148 * 128 * clocks["sm_mhz"] * 1e6
             roofline["fp32_fma"] = {"fma_per_param": 1600, "achieved_tfma": fma / 1e12,
                                     "peak_tfma_at_sampled_clock": peak_fma / 1e12, "frac": fma / peak_fma}
         cpu = None
-        if not args.no_cpu_baseline and world == 1:
+        if headline and not args.no_cpu_baseline and world == 1:
             v, cores, desc, _ = run_cpu_oracle(args, shapes, args.cpu_sample_steps)
             cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
+        cfg = config_of(args, shapes, world)
+        if replica is not None:
+            cfg["replica_check"] = replica
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_of(args, shapes, world),
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
+    ok = replica is None or replica["equal"]
+    # free this configuration's memory before the next one is built
+    del opt, shard, params, pool
+    torch.cuda.empty_cache()
+    return line, ok
+
+
+# the other benchmark configurations, measured after the headline: (name, workload, optimizer, extra arguments, timed steps)
+EXTRA_CONFIGS = [
+    ("velo/gpt2_medium", "gpt2_medium", "velo", [], 50),
+    ("celo2/celo2_4096/ns_off", "celo2_4096", "celo2", ["--no-orthogonalize"], 100),
+    ("celo2/celo2_4096/ns_on", "celo2_4096", "celo2", [], 20),
+    ("elo_celo2/vit_b16/ns_off", "vit_b16", "elo_celo2", ["--no-orthogonalize"], 100),
+    ("elo_celo2/vit_b16/ns_on", "vit_b16", "elo_celo2", [], 20),
+    ("celo2/llama3_8b/ns_off", "llama3_8b", "celo2", ["--no-orthogonalize"], 3),
+]
+
+
+def compact(name, line):
+    r = line["roofline"]
+    return {"name": name, "workload": line["config"]["workload"], "ms_per_step": line["ms_per_step"], "steps": line["steps"],
+            "value": line["value"], "unit": UNIT, "orthogonalize": line["config"]["orthogonalize"],
+            "exchange": line["config"]["exchange"], "cache": line["config"]["cache"],
+            "replica_check": line["config"].get("replica_check"),
+            "roofline": {"step_frac": r["step"]["frac"], "step_bytes_per_param": r["step"]["algorithmic_bytes_per_param"],
+                         "kernel": r["kernel"], "kernel_frac": r["frac"], "kernel_avg_launch_ms": r["avg_launch_ms"],
+                         "phase_share": r["phase_share"]},
+            "gpu_launches": line["gpu_launches"], "clocks": line["clocks"]}
+
+
+def run_b200(args):
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    try:
+        line, ok = measure(args, dev, world, rank, local, headline=True)
+    except MemoryError as e:
+        raise SystemExit(str(e))
+    all_ok = ok
+    default_run = args.workload == "llama3_8b" and args.optimizer == "adafaclo" and args.layers is None
+    if default_run and not args.no_extra:
+        extras = []
+        for name, workload, optimizer, more, steps in EXTRA_CONFIGS:
+            sub = copy.copy(args)
+            sub.workload, sub.optimizer, sub.steps, sub.warmup = workload, optimizer, steps, 3
+            sub.no_orthogonalize = "--no-orthogonalize" in more
+            if workload == "llama3_8b" and world == 1:
+                # 8.03 G parameters with the CELO2 family's 20 B/param of state do not fit one GPU: 16 of the 32 layers
+                sub.layers = 16
+                name += "/16_layers"
+            try:
+                sub_line, ok = measure(sub, dev, world, rank, local, headline=False)
+                all_ok = all_ok and ok
+                if rank == 0:
+                    extras.append(compact(name, sub_line))
+            except Exception as e:  # a configuration that cannot run here is reported, not fatal to the headline
+                if rank == 0:
+                    extras.append({"name": name, "error": f"{type(e).__name__}: {e}"[:300]})
+                torch.cuda.empty_cache()
+        if rank == 0:
+            line["extra_configs"] = extras
+    if rank == 0:
+        if world == 1 and not args.no_reference_cuda:
+            line["reference_cuda"] = run_reference_cuda(dev)
         emit(line)
     if world > 1:
         dist.destroy_process_group()
+    if not all_ok:
+        raise SystemExit("replica_check failed: the ranks' parameter buffers differ after the last step")
+
+
+def run_reference_cuda(dev):
+    """The reference's OWN CUDA kernels (built from its sources into oracle/_ref/ by oracle/build_ref.py) timed on
+    this GPU next to this library, on a bounded sample: the "kernel to beat"."""
+    probed = [os.path.join(ROOT, "oracle", "_ref", n + ".so") for n in ("cuda_lo", "celo2_cuda_kernel", "velo_cuda_kernel")]
+    if not all(os.path.exists(p) for p in probed):
+        return {"status": "unavailable", "why": "the reference's CUDA extensions were not built into oracle/_ref/",
+                "probed": probed}
+    try:
+        from oracle import ref_cuda
+        return ref_cuda.time_against_library(dev, seeded_networks)
+    except Exception as e:
+        return {"status": "unavailable", "why": f"{type(e).__name__}: {e}"[:300], "probed": probed}
 
 
 def emit(line):

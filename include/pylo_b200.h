@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define PYLO_B200_ABI_VERSION 6
+#define PYLO_B200_ABI_VERSION 7
 
 /* optimizer families (which feature set / network geometry a launch uses) */
 #define PYLO_FAM_ADAFAC 0 /* AdafacLO_CUDA, ELO_CUDA: 28+11 features, 39-32-32-2 */
@@ -81,7 +81,7 @@ typedef struct pylo_tensor_desc {
   float* h_a;     /* workspace [La][H] (ADAFAC) or [La][H][2] (CELO2, VELO): first-layer term of the "a" features (+ bias) */
   float* h_b;     /* workspace [H][Lb]: first-layer term of the "b" features */
   float* closed;  /* workspace [PYLO_STAT_STRIDE]: closed-form sums of squares of vector features */
-  float* sums;    /* workspace [PYLO_STAT_STRIDE]: per-tensor sums (features, then VeLO statistics) */
+  float* sums;    /* workspace [48]: per-tensor sums (30 feature slots, 8 VeLO statistics, their 8 low-order parts) */
   float* wfold;   /* workspace [PYLO_WFOLD_STRIDE]: network with normalisers folded in */
   float* tile_part; /* workspace [n_tiles][PYLO_STAT_STRIDE] */
   float* out;     /* CELO2: raw step output [n]; else NULL */
@@ -149,6 +149,28 @@ typedef struct pylo_step_params {
 int pylo_b200_abi_version(void);
 int pylo_b200_sizeof_desc(void);
 int pylo_b200_sizeof_params(void);
+
+/* Workspace sizing, for hosts that fill pylo_tensor_desc themselves.  The reference needs no counterpart: its
+ * only scratch is the second_moment[28|30] tensor its Python classes allocate per call
+ * (AdafacLO_cuda.py:376-380, CELO2_cuda.py:287-291, velo_cuda.py:731-735).
+ *
+ * pylo_b200_workspace_layout fills, for one tensor of the given family, traversal mode and geometry, the size
+ * in floats of every workspace sub-buffer that pylo_tensor_desc points at (0 where the mode does not use it),
+ * and the phase-A tiling (rb, n_strips, n_cb) and the number of element-wise tiles that go into the descriptor.
+ * A unit of element-wise work that is a slice of a tensor (vec_elementwise = 1) owns only the last three
+ * sub-buffers (sums, wfold, tile_part), sized with n = the slice's elements, plus a zero-filled `closed`; the
+ * others belong to its tensor.  Every sub-buffer must start on a 256-byte boundary and the whole workspace
+ * must be zero before the first step.
+ * pylo_b200_workspace_bytes adds the sizes up, each rounded up to 256 bytes: tensor_part != 0 counts f_a .. closed,
+ * unit_part != 0 counts sums, wfold, tile_part.  Host-only; nothing is launched. */
+typedef struct pylo_ws_layout {
+  int64_t f_a, f_b, sum_a, sum_b, fx, part_a, part_b, h_a, h_b, closed; /* per tensor */
+  int64_t sums, wfold, tile_part;                                         /* per unit of element-wise work */
+  int32_t rb, n_strips, n_cb, n_tiles;
+} pylo_ws_layout;
+int pylo_b200_workspace_layout(int family, int mode, int64_t n, int64_t La, int64_t Lb, int32_t X, int32_t Y,
+                               pylo_ws_layout* out);
+int64_t pylo_b200_workspace_bytes(const pylo_ws_layout* layout, int tensor_part, int unit_part);
 
 /* Sum of squares of every gradient (CELO2_cuda.py:180-188, ELO_cuda.py:150-158).
  * items: one per tensor with a gradient (all of them, AdamW-routed ones included);

@@ -34,6 +34,14 @@ what ``VeLO_naive`` shares with ``VeLO_CUDA``.
 
 State layout is the ``*_CUDA`` one (decay axis leading), which is also the
 resume format of the product classes, so states can be compared key by key.
+
+Every oracle class takes ``device=`` (default CPU) and ``ref_kernel=``.  With a
+``ref_kernel`` the Python-side state update restated here runs on that device
+and the fused part of the step is done by the REFERENCE'S OWN CUDA extension
+(built from the reference's sources by ``oracle/build_ref.py``, loaded by
+``oracle/ref_cuda.py``) instead of the restatement in
+``_feature_moments_and_apply``: the reference's ``*_CUDA`` path end to end, used
+on a GPU as a second checker and as the timed "kernel to beat".
 """
 
 from __future__ import annotations
@@ -231,9 +239,13 @@ class AdafacLOOracle:
         clip_norm=1.0,
         variant="cuda",
         dtype=torch.float32,
+        device="cpu",
+        ref_kernel=None,
     ):
         self.dtype = dtype
-        self.w = [w.detach().to(dtype).cpu() for w in weights]
+        self.device = torch.device(device)
+        self.ref_kernel = ref_kernel  # cuda_lo.learned_optimizer_kernel of the reference, or None
+        self.w = [w.detach().to(dtype).to(self.device).contiguous() for w in weights]
         self.lr, self.step_mult, self.exp_mult, self.wd = lr, step_mult, exp_mult, weight_decay
         self.elo, self.clip_grad, self.clip_norm = elo, clip_grad, clip_norm
         if elo:
@@ -244,24 +256,26 @@ class AdafacLOOracle:
             self.beta_m = beta_m if beta_m is not None else decay_reparam((0.9, 0.99, 0.999), (0.15216392, 0.14245212, 0.06812963))
             self.beta_rms = beta_rms if beta_rms is not None else decay_reparam((0.999,), (0.01079706,))
             self.beta_fac = beta_fac if beta_fac is not None else decay_reparam((0.9, 0.99, 0.999), (0.18621896, -0.10864615, -0.06185547))
+        self.beta_m, self.beta_rms, self.beta_fac = (b.to(self.device) for b in (self.beta_m, self.beta_rms, self.beta_fac))
         self.variant = Variant(variant)
         self.state: List[Dict] = []
 
     def _init_state(self, g):
         shape = tuple(g.shape)
         st = {"step": 0.0}
+        kw = dict(dtype=self.dtype, device=self.device)
         fd = factored_dims_sorted(shape)
         if fd is not None:
             dc, dr = fd
             rs, cs = list(shape), list(shape)
             rs[dr], cs[dc] = 1, 1
-            st["exp_avg_sq_r"] = torch.zeros([3] + rs, dtype=self.dtype)
-            st["exp_avg_sq_c"] = torch.zeros([3] + cs, dtype=self.dtype)
+            st["exp_avg_sq_r"] = torch.zeros([3] + rs, **kw)
+            st["exp_avg_sq_c"] = torch.zeros([3] + cs, **kw)
         else:
-            st["exp_avg_sq_r"] = torch.zeros((3,) + shape, dtype=self.dtype)
-            st["exp_avg_sq_c"] = torch.zeros((3,) + shape, dtype=self.dtype)
-        st["exp_avg_sq"] = torch.zeros(shape, dtype=self.dtype)
-        st["exp_avg"] = torch.zeros((3,) + shape, dtype=self.dtype)
+            st["exp_avg_sq_r"] = torch.zeros((3,) + shape, **kw)
+            st["exp_avg_sq_c"] = torch.zeros((3,) + shape, **kw)
+        st["exp_avg_sq"] = torch.zeros(shape, **kw)
+        st["exp_avg"] = torch.zeros((3,) + shape, **kw)
         return st
 
     def _mlp(self, x):
@@ -316,6 +330,24 @@ class AdafacLOOracle:
             rf_m = torch.pow(fr + 1e-6, -0.5) if self.variant.naive else rf_g
             cf_g = cf_m = None
         st["exp_avg"].lerp_(g[None, ...], 1 - _lead(self.beta_m, g.dim()).to(dt))
+
+        if self.ref_kernel is not None:
+            # AdafacLO_cuda.py:378-405 / ELO_cuda.py:262-286: the reference's fused kernel does the rest
+            if fd is not None:
+                row_factor, col_factor, kdc, kdr, vector_like = rf, cf, fd[0], fd[1], 0
+            else:
+                row_factor = safe_rsqrt(st["exp_avg_sq_r"] + 1e-9)
+                col_factor, kdc, kdr, vector_like = torch.ones_like(row_factor), 0, 0, 1
+            second = torch.zeros(28, dtype=dt, device=self.device)
+            p_before = p.clone() if (self.elo and self.wd > 0) else None
+            self.ref_kernel(g.contiguous(), p, st["exp_avg"], st["exp_avg_sq"], st["exp_avg_sq_r"], st["exp_avg_sq_c"],
+                            row_factor.contiguous(), col_factor.contiguous(), second, *self.w, float(self.lr),
+                            1.0 if self.elo else float(self.step_mult), float(self.exp_mult), 1e-6, st["step"] - 1.0, 0.0,
+                            int(kdc), int(kdr), int(vector_like))
+            st["second_moment"] = second
+            if self.wd > 0:
+                p.add_(p_before if self.elo else p, alpha=-self.wd * self.lr)
+            return
 
         gf, pf = g.reshape(-1), p.reshape(-1)
         m = st["exp_avg"].reshape(3, -1)
@@ -414,9 +446,13 @@ class CELO2Oracle:
         shared_adam=False,
         is_embedding: Optional[Sequence[bool]] = None,
         dtype=torch.float32,
+        device="cpu",
+        ref_kernel=None,
     ):
         self.dtype = dtype
-        self.w = [w.detach().to(dtype).cpu() for w in weights]
+        self.device = torch.device(device)
+        self.ref_kernel = ref_kernel  # celo2_cuda_kernel.celo2_kernel of the reference, or None
+        self.w = [w.detach().to(dtype).to(self.device).contiguous() for w in weights]
         self.lr, self.wd = lr, weight_decay
         self.adam_lr_mult = adam_lr_mult
         self.adam_wd = adam_weight_decay if adam_weight_decay is not None else weight_decay
@@ -424,7 +460,7 @@ class CELO2Oracle:
         self.adam_eps = adam_eps
         self.use_adamw_for_1d = use_adamw_for_1d
         self.orthogonalize, self.clip_grad, self.clip_norm = orthogonalize, clip_grad, clip_norm
-        self.beta_m, self.beta_rms, self.beta_fac = clamp_decays(beta_m), clamp_decays(beta_rms), clamp_decays(beta_fac)
+        self.beta_m, self.beta_rms, self.beta_fac = (clamp_decays(b).to(self.device) for b in (beta_m, beta_rms, beta_fac))
         self.exp_mult, self.rmsmult = exp_mult, rmsmult
         self.ns = (tuple(float(c) for c in ns_coeffs), ns_iters, ns_eps)
         self.grad_clip_val = grad_clip_val
@@ -440,15 +476,16 @@ class CELO2Oracle:
         return h @ w_out + b_out
 
     def _init_lo_state(self, st, shape):
-        st["mom"] = torch.zeros((3,) + shape, dtype=self.dtype)
-        st["rms"] = torch.zeros(shape, dtype=self.dtype)
+        kw = dict(dtype=self.dtype, device=self.device)
+        st["mom"] = torch.zeros((3,) + shape, **kw)
+        st["rms"] = torch.zeros(shape, **kw)
         fd = factored_dims_argsort(shape)
         if fd is not None:
             dc, dr = fd
             rs, cs = list(shape), list(shape)
             rs[dr], cs[dc] = 1, 1
-            st["fac_r"] = torch.zeros([3] + rs, dtype=self.dtype)
-            st["fac_c"] = torch.zeros([3] + cs, dtype=self.dtype)
+            st["fac_r"] = torch.zeros([3] + rs, **kw)
+            st["fac_c"] = torch.zeros([3] + cs, **kw)
 
     def step(self, params, grads):
         if not self.state:
@@ -518,6 +555,15 @@ class CELO2Oracle:
         dc, dr = fd
         grad_sqr = g * g + 1e-30
         fac_r, fac_c, rf, cf = _update_factored(st, grad_sqr, fd, self.beta_fac, "fac_r", "fac_c", dc + 1)
+        if self.ref_kernel is not None:
+            # CELO2_cuda.py:301-339: the reference's fused kernel writes the raw step, the tail stays torch
+            second = torch.zeros(self.FEAT, dtype=dt, device=self.device)
+            step = torch.empty_like(p)
+            self.ref_kernel(g.contiguous(), p, st["mom"], st["rms"], fac_r, fac_c, rf.contiguous(), cf.contiguous(), second,
+                            *self.w, step, float(self.exp_mult), int(dc), int(dr), 0)
+            st["second_moment"] = second
+            self._tail(p, step, st)
+            return
         rfb, cfb = _bcast_flat(rf, shape), _bcast_flat(cf, shape)
         fr, fc = _bcast_flat(fac_r, shape), _bcast_flat(fac_c, shape)
         gf, pf = g.reshape(-1), p.reshape(-1)
@@ -555,7 +601,10 @@ class CELO2Oracle:
             gsize = shape[-1] * shape[-2]
             groups = (torch.arange(n, dtype=torch.int64) // gsize, n // gsize, gsize)
         st["second_moment"] = _feature_moments_and_apply(n, self.FEAT, build, 1e-9, self._mlp, consume, groups)
-        step = step_flat.view(shape)
+        self._tail(p, step_flat.view(shape), st)
+
+    def _tail(self, p, step, st):
+        """Newton-Schulz, the second-moment normaliser over the last two axes, the update (CELO2_cuda.py:331-339)."""
         st["raw_step"] = step.clone()
         if self.orthogonalize:
             step = newton_schulz(step, *self.ns)
@@ -629,16 +678,20 @@ class VeLOOracle:
         num_steps=10000,
         variant="cuda",
         dtype=torch.float32,
+        device="cpu",
+        ref_kernel=None,
     ):
         self.dtype = dtype
-        self.rnn = {k: v.detach().to(dtype).cpu() for k, v in rnn.items()}
-        self.bank = bank.detach().to(dtype).cpu()
+        self.device = torch.device(device)
+        self.ref_kernel = ref_kernel  # velo_cuda_kernel.velo_kernel_simple of the reference, or None
+        self.rnn = {k: v.detach().to(dtype).to(self.device) for k, v in rnn.items()}
+        self.bank = bank.detach().to(dtype).to(self.device)
         self.lr, self.exp_mult, self.step_mult, self.wd = lr, exp_mult, step_mult, weight_decay
         self.num_steps = num_steps
         zero3, zero1 = (0.0, 0.0, 0.0), (0.0,)
-        self.beta_m = decay_reparam((0.9, 0.99, 0.999), zero3)
-        self.beta_rms = decay_reparam((0.999,), zero1)
-        self.beta_fac = decay_reparam((0.9, 0.99, 0.999), zero3)
+        self.beta_m = decay_reparam((0.9, 0.99, 0.999), zero3).to(self.device)
+        self.beta_rms = decay_reparam((0.999,), zero1).to(self.device)
+        self.beta_fac = decay_reparam((0.9, 0.99, 0.999), zero3).to(self.device)
         self.variant = Variant(variant)
         self.loss_buffer = LossBuffer(num_steps)
         self.group_step = 0
@@ -646,22 +699,22 @@ class VeLOOracle:
         for idx, shape in enumerate(shapes):
             shape = tuple(shape)
             st = {"layer_idx": idx}
-            st["mom"] = torch.zeros((3,) + shape, dtype=dtype)
-            st["rms"] = torch.zeros((1,) + shape, dtype=dtype)
+            st["mom"] = torch.zeros((3,) + shape, dtype=dtype, device=self.device)
+            st["rms"] = torch.zeros((1,) + shape, dtype=dtype, device=self.device)
             fd = factored_dims_velo(shape)
             if fd is not None:
                 dc, dr = fd
                 rs, cs = list(shape), list(shape)
                 rs[dr], cs[dc] = 1, 1
-                st["fac_vec_row"] = torch.zeros([3] + rs, dtype=dtype)
-                st["fac_vec_col"] = torch.zeros([3] + cs, dtype=dtype)
-                st["fac_vec_v"] = torch.zeros(0, dtype=dtype)
+                st["fac_vec_row"] = torch.zeros([3] + rs, dtype=dtype, device=self.device)
+                st["fac_vec_col"] = torch.zeros([3] + cs, dtype=dtype, device=self.device)
+                st["fac_vec_v"] = torch.zeros(0, dtype=dtype, device=self.device)
             else:
-                st["fac_vec_row"] = torch.zeros(0, dtype=dtype)
-                st["fac_vec_col"] = torch.zeros(0, dtype=dtype)
-                st["fac_vec_v"] = torch.zeros((3,) + shape, dtype=dtype)
+                st["fac_vec_row"] = torch.zeros(0, dtype=dtype, device=self.device)
+                st["fac_vec_col"] = torch.zeros(0, dtype=dtype, device=self.device)
+                st["fac_vec_v"] = torch.zeros((3,) + shape, dtype=dtype, device=self.device)
             rank = sum(1 for d in shape if d > 1)
-            st["rank_onehot"] = torch.nn.functional.one_hot(torch.tensor(rank), num_classes=5).to(dtype)
+            st["rank_onehot"] = torch.nn.functional.one_hot(torch.tensor(rank), num_classes=5).to(dtype).to(self.device)
             self.state.append(st)
         T = len(shapes)
         self.lstm_hidden_state = (self.rnn["h0"].repeat(T, 1), self.rnn["c0"].repeat(T, 1))
@@ -676,7 +729,7 @@ class VeLOOracle:
         var_m = ((m - mean_m) ** 2).mean(dim=1)
         mean_rms = rms.mean(dim=1)
         var_rms = ((rms - mean_m) ** 2).mean(dim=1)
-        out = torch.empty(30, dtype=dt)
+        out = torch.empty(30, dtype=dt, device=self.device)
         out[0:9] = fraction_left
         out[9:18] = loss_features
         out[18:19] = clip_log_abs(mean_rms, 10.0)
@@ -702,8 +755,8 @@ class VeLOOracle:
     def step(self, params, grads, loss):
         dt = self.dtype
         self.loss_buffer.update(loss)
-        loss_feat = self.loss_buffer.features().to(dt)
-        fraction_left = fractional_tanh_embed(self.group_step / self.num_steps).to(dt)
+        loss_feat = self.loss_buffer.features().to(dt).to(self.device)
+        fraction_left = fractional_tanh_embed(self.group_step / self.num_steps).to(dt).to(self.device)
         feats = [self._tensor_features(p, st, fraction_left, loss_feat) for p, st in zip(params, self.state)]
         x = torch.flip(torch.stack(feats), [0])
         self.rnn_inputs = x
@@ -741,6 +794,23 @@ class VeLOOracle:
         w_h, b_h = w[124:140].view(4, 4), w[140:144]
         w_out, b_out = w[144:156].view(3, 4), w[156:159]
         st["mlp_weights"] = w.clone()
+
+        if self.ref_kernel is not None:
+            # velo_cuda.py:694-755: factors from the updated accumulators, then the reference's fused kernel
+            if fd is not None:
+                row_factor, col_factor, vr, vc, kdc, kdr, vector_like = rf, cf, fac_r, fac_c, fd[0], fd[1], 0
+            else:
+                vr = vc = st["fac_vec_v"]
+                row_factor = safe_rsqrt(vr + 1e-9)
+                col_factor, kdc, kdr, vector_like = torch.ones_like(row_factor), 0, 0, 1
+            second = torch.zeros(self.FEAT, dtype=dt, device=self.device)
+            self.ref_kernel(g.contiguous(), p, st["mom"], st["rms"], row_factor.contiguous(), col_factor.contiguous(), vr, vc,
+                            second, w_in.contiguous(), b_in.contiguous(), w_h.contiguous(), b_h.contiguous(),
+                            w_out.contiguous(), b_out.contiguous(), float(self.lr * float(lr_mult[-(1 + layer)])),
+                            float(self.step_mult), float(self.exp_mult), 1e-6, float(self.wd), int(kdc), int(kdr),
+                            int(vector_like))
+            st["second_moment"] = second
+            return
 
         gf, pf = g.reshape(-1), p.reshape(-1)
         m = st["mom"].reshape(3, -1)

@@ -16,7 +16,7 @@ SUMS_STRIDE = 48
 TILE_ELEMS = 16384
 A_COLS = 1024
 WFOLD_STRIDE = 2432
-ABI_VERSION = 6
+ABI_VERSION = 7
 
 FAM_ADAFAC, FAM_CELO2, FAM_VELO = 0, 1, 2
 MODE_FAST2D, MODE_GENERIC, MODE_VEC1D = 0, 1, 2
@@ -59,6 +59,13 @@ class StepParams(C.Structure):
     ]
 
 
+class WsLayout(C.Structure):
+    """pylo_ws_layout: sizes in floats of a tensor's workspace sub-buffers and its phase-A / element-wise tiling."""
+    _fields_ = [(name, C.c_int64) for name in (
+        "f_a", "f_b", "sum_a", "sum_b", "fx", "part_a", "part_b", "h_a", "h_b", "closed", "sums", "wfold", "tile_part")] + [
+        (name, C.c_int32) for name in ("rb", "n_strips", "n_cb", "n_tiles")]
+
+
 class VeloRnn(C.Structure):
     _fields_ = [(name, C.c_void_p) for name in (
         "mix2_w", "mix2_b", "fmix_w", "fmix_b", "lstm_w", "lstm_b", "ctrl_w", "ctrl_b", "step_w", "step_b",
@@ -85,6 +92,8 @@ def _load():
         "pylo_b200_abi_version": [],
         "pylo_b200_sizeof_desc": [],
         "pylo_b200_sizeof_params": [],
+        "pylo_b200_workspace_layout": [i32, i32, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.POINTER(WsLayout)],
+        "pylo_b200_workspace_bytes": [C.POINTER(WsLayout), i32, i32],
         "pylo_b200_grad_sumsq": [vp, vp, i32, vp, vp, vp],
         "pylo_b200_grad_sumsq_static": [vp, vp, i32, vp, vp],
         "pylo_b200_rowcol_sums": [vp, vp, i32, vp, i32, vp, i32, C.POINTER(StepParams), vp],
@@ -107,7 +116,7 @@ def _load():
     for name, argtypes in sigs.items():
         fn = getattr(lib, name)  # AttributeError if a declared symbol is missing
         fn.argtypes = argtypes
-        fn.restype = C.c_int
+        fn.restype = C.c_int64 if name == "pylo_b200_workspace_bytes" else C.c_int
     if lib.pylo_b200_abi_version() != ABI_VERSION:
         raise ImportError("libpylo_b200.so was built from a different ABI version; rebuild it")
     if lib.pylo_b200_sizeof_desc() != DESC_DTYPE.itemsize or lib.pylo_b200_sizeof_params() != C.sizeof(StepParams):
@@ -121,6 +130,13 @@ lib, EXPORTED = _load()
 TC_WORKERS = {"tf32": 148 * 5, "fp16": 148 * 6}  # warpgroups a tensor-core apply kernel runs at once (5 or 6 per SM)
 STATIC_SCRATCH_TILES = 65536
 ERR_STATIC_SCRATCH_TOO_SMALL = -4
+
+
+def workspace_layout(family, mode, n, La=0, Lb=0, X=0, Y=0) -> WsLayout:
+    """``pylo_b200_workspace_layout`` for one tensor (or one slice unit); raises if the library rejects the geometry."""
+    out = WsLayout()
+    check(lib.pylo_b200_workspace_layout(family, mode, n, La, Lb, X, Y, C.byref(out)), "workspace_layout")
+    return out
 
 
 def check(code, what):

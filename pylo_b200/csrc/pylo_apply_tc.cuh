@@ -20,8 +20,9 @@
 //     another's: five warpgroups per CTA, one CTA per SM; every warpgroup is an independent worker
 //     with its own work items, its own copy of the weights in shared memory, its own accumulator
 //     columns and its own barriers, so the warpgroups drift apart instead of marching in step.
-// Every wait on the tensor core is bounded: on a timeout the kernel records it in *status and goes on
-// (with wrong values) to the end, where it frees its tensor memory.
+// Every wait on the tensor core is bounded.  A thread whose wait ran out records it in *status, stops waiting
+// and stops storing (its parameters, and their copies on the peers, keep their old values), and goes on to
+// the end, where the kernel frees its tensor memory.  A launch that finds *status already set stores nothing.
 #pragma once
 
 #ifndef TC_WGS
@@ -144,6 +145,7 @@ struct TcWgSmem {
 struct TcSmem {
   TcWgSmem wg[TC_WGS];
   uint32_t tmem_base;
+  int poisoned;  // the status word at launch: non-zero means an earlier launch reported a timed-out wait
 };
 
 // the six vector features of one index of the "a" or "b" vector, feature j of 6: fac[j] (j < 3) or rsqrt(fac[j-3] + 1e-8)
@@ -169,10 +171,14 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
   TcWgSmem& sm = smem.wg[wg];
   if (col == 0) mbar_init(&sm.bar, 1);
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  if (tid == 32) smem.poisoned = status ? *reinterpret_cast<volatile int*>(status) : 0;
   if (warp == 0) { tc_alloc(&smem.tmem_base, 512); tc_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // A launch that finds the status word already set writes nothing (no parameter, no peer store): the
+  // parameters stay as the last good step left them until the host has looked at the error and cleared it.
+  const int n_items = smem.poisoned ? 0 : n_ttiles;
   const uint32_t t_wg = smem.tmem_base + wg * TC_WG_TMEM;               // lane 0 of this warpgroup's columns
   const uint32_t t_lane = t_wg + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes
   const uint32_t tA = t_lane, tD = t_lane + 64;
@@ -191,7 +197,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
   bool timed_out = false;
   int loaded = -1;
   // every warpgroup is a worker of its own: it takes every (gridDim.x * TC_WGS)-th work item
-  for (int t = blockIdx.x * TC_WGS + wg; t < n_ttiles; t += gridDim.x * TC_WGS) {
+  for (int t = blockIdx.x * TC_WGS + wg; t < n_items; t += gridDim.x * TC_WGS) {
     const pylo_atile ct = ttiles[t];
     const pylo_tensor_desc& d = descs[ct.tensor];
     const int X = d.X, Y = d.Y;
@@ -337,7 +343,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
         tc_commit(&sm.bar);
       }
       __syncwarp();
-      if (!mbar_wait(&sm.bar, parity)) timed_out = true;
+      if (!timed_out && !mbar_wait(&sm.bar, parity)) timed_out = true;
       parity ^= 1;
       tc_fence_after();
       // ---- hidden layer 1: relu, split, back into tensor memory as operand A of the second layer
@@ -377,7 +383,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
         tc_commit(&sm.bar);
       }
       __syncwarp();
-      if (!mbar_wait(&sm.bar, parity)) timed_out = true;
+      if (!timed_out && !mbar_wait(&sm.bar, parity)) timed_out = true;
       parity ^= 1;
       tc_fence_after();
       // ---- hidden layer 2 (relu) and the two output heads as packed dot products over unit pairs
@@ -404,7 +410,7 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
         unpack2(add2(od[0], od[1]), a, b);
         unpack2(add2(om[0], om[1]), c, dd);
         const float o0 = (a + b) + sm.w3[64], o1 = (c + dd) + sm.w3[65];
-        if (colok) {
+        if (colok && !timed_out) {  // after a wait that ran out the accumulators are not to be trusted: keep the old value
           const Fin fin{ic.exp_mult, ic.step_mult, ic.wd, ic.lr, ic.lr_eff, 1.0f, ic.wd_mode};
           const float pn = finish<PYLO_FAM_ADAFAC>(cp, o0, o1, fin);
           const int64_t idx = (int64_t)x * Y + y;

@@ -59,6 +59,7 @@ struct ThWgSmem {
 struct ThSmem {
   ThWgSmem wg[TH_WGS];
   uint32_t tmem_base;
+  int poisoned;  // the status word at launch: non-zero means an earlier launch reported a timed-out wait
 };
 
 // the pair (2c, 2c+1) of the six features of a vector entry: fac[0..2], then rsqrt(fac[0..2] + 1e-8)
@@ -78,10 +79,14 @@ __global__ void __launch_bounds__(TH_NT, 1) k_apply_adafac_tc16(const pylo_tenso
   ThWgSmem& sm = smem.wg[wg];
   if (col == 0) mbar_init(&sm.bar, 1);
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  if (tid == 32) smem.poisoned = status ? *reinterpret_cast<volatile int*>(status) : 0;
   if (warp == 0) { tc_alloc(&smem.tmem_base, 512); tc_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // A launch that finds the status word already set writes nothing (no parameter, no peer store): the
+  // parameters stay as the last good step left them until the host has looked at the error and cleared it.
+  const int n_items = smem.poisoned ? 0 : n_ttiles;
   const uint32_t t_wg = smem.tmem_base + wg * TH_WG_TMEM;               // lane 0 of this warpgroup's columns
   const uint32_t t_lane = t_wg + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes
   const uint32_t tA = t_lane, tD = t_lane + 32;
@@ -99,7 +104,7 @@ __global__ void __launch_bounds__(TH_NT, 1) k_apply_adafac_tc16(const pylo_tenso
   uint32_t parity = 0;
   bool timed_out = false;
   int loaded = -1;
-  for (int t = blockIdx.x * TH_WGS + wg; t < n_ttiles; t += gridDim.x * TH_WGS) {
+  for (int t = blockIdx.x * TH_WGS + wg; t < n_items; t += gridDim.x * TH_WGS) {
     const pylo_atile ct = ttiles[t];
     const pylo_tensor_desc& d = descs[ct.tensor];
     const int X = d.X, Y = d.Y;
@@ -252,7 +257,7 @@ __global__ void __launch_bounds__(TH_NT, 1) k_apply_adafac_tc16(const pylo_tenso
         tc_commit(&sm.bar);
       }
       __syncwarp();
-      if (!mbar_wait(&sm.bar, parity)) timed_out = true;
+      if (!timed_out && !mbar_wait(&sm.bar, parity)) timed_out = true;
       parity ^= 1;
       tc_fence_after();
       // ---- hidden layer 1: relu, split into halves, back into tensor memory as operand A of the second layer
@@ -285,7 +290,7 @@ __global__ void __launch_bounds__(TH_NT, 1) k_apply_adafac_tc16(const pylo_tenso
         tc_commit(&sm.bar);
       }
       __syncwarp();
-      if (!mbar_wait(&sm.bar, parity)) timed_out = true;
+      if (!timed_out && !mbar_wait(&sm.bar, parity)) timed_out = true;
       parity ^= 1;
       tc_fence_after();
       // ---- hidden layer 2 (relu) and the two output heads as packed dot products over unit pairs
@@ -312,7 +317,7 @@ __global__ void __launch_bounds__(TH_NT, 1) k_apply_adafac_tc16(const pylo_tenso
         unpack2(add2(od[0], od[1]), a, b);
         unpack2(add2(om[0], om[1]), c, dd);
         const float o0 = (a + b) + sm.w3[64], o1 = (c + dd) + sm.w3[65];
-        if (colok) {
+        if (colok && !timed_out) {  // after a wait that ran out the accumulators are not to be trusted: keep the old value
           const Fin fin{ic.exp_mult, ic.step_mult, ic.wd, ic.lr, ic.lr_eff, 1.0f, ic.wd_mode};
           const float pn = finish<PYLO_FAM_ADAFAC>(cp, o0, o1, fin);
           const int64_t idx = (int64_t)x * Y + y;

@@ -1563,15 +1563,18 @@ __global__ void __launch_bounds__(160) k_velo_mix(const pylo_velo_rnn r) {
 // ================================================================================================
 // C ABI
 // ================================================================================================
-static int g_sm_count = 0;
+// Opt-in limits and caches are kept per device: the library may be used on every GPU of a box from one process.
+#define PYLO_MAX_DEVICES 64
+static int g_sm_count[PYLO_MAX_DEVICES] = {0};
 static int sm_count() {
-  if (g_sm_count == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-    if (g_sm_count <= 0) g_sm_count = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= PYLO_MAX_DEVICES) return 148;
+  if (g_sm_count[dev] == 0) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    g_sm_count[dev] = n > 0 ? n : 148;
   }
-  return g_sm_count;
+  return g_sm_count[dev];
 }
 static int grid_for(int n_items, int ctas_per_sm) {
   const int cap = sm_count() * ctas_per_sm;
@@ -1581,7 +1584,6 @@ static int launch_status() { return (int)cudaGetLastError(); }
 
 // Opt a kernel in to more than 48 KB of dynamic shared memory, once per device (the attribute belongs to the
 // device's copy of the function); flags[] is the caller's per-kernel record.
-#define PYLO_MAX_DEVICES 64
 template <class K>
 static int allow_dynamic_smem(K kernel, int bytes, bool (&flags)[PYLO_MAX_DEVICES]) {
   int dev = 0;
@@ -1604,6 +1606,50 @@ extern "C" {
 int pylo_b200_abi_version(void) { return PYLO_B200_ABI_VERSION; }
 int pylo_b200_sizeof_desc(void) { return (int)sizeof(pylo_tensor_desc); }
 int pylo_b200_sizeof_params(void) { return (int)sizeof(pylo_step_params); }
+
+int pylo_b200_workspace_layout(int family, int mode, int64_t n, int64_t La, int64_t Lb, int32_t X, int32_t Y,
+                               pylo_ws_layout* out) {
+  CHECK_ARG(out && n > 0);
+  CHECK_ARG(family == PYLO_FAM_ADAFAC || family == PYLO_FAM_CELO2 || family == PYLO_FAM_VELO);
+  CHECK_ARG(mode == PYLO_MODE_FAST2D || mode == PYLO_MODE_GENERIC || mode == PYLO_MODE_VEC1D);
+  const int64_t H = family == PYLO_FAM_ADAFAC ? 32 : (family == PYLO_FAM_CELO2 ? 8 : 4);
+  pylo_ws_layout w = {};
+  if (mode != PYLO_MODE_VEC1D) {
+    CHECK_ARG(La > 0 && Lb > 0);
+    w.f_a = 3 * La; w.f_b = 3 * Lb; w.sum_a = La; w.sum_b = Lb;
+  }
+  if (mode == PYLO_MODE_FAST2D) {
+    CHECK_ARG(X > 0 && Y > 0 && Y % 4 == 0 && La == X && Lb == Y);
+    int rb = (((X + 127) / 128 + 7) / 8) * 8;  // rows per strip: about X / 128, a multiple of 8, within [32, 128]
+    rb = rb < 32 ? 32 : (rb > 128 ? 128 : rb);
+    w.rb = rb;
+    w.n_strips = (X + rb - 1) / rb;
+    w.n_cb = (Y + PYLO_A_COLS - 1) / PYLO_A_COLS;
+    w.fx = 4 * La;
+    w.part_a = (int64_t)X * w.n_cb;
+    w.part_b = (int64_t)w.n_strips * Y;
+    w.h_a = La * H * 2;
+    w.h_b = Lb * H;
+  }
+  w.closed = PYLO_STAT_STRIDE;
+  w.n_tiles = (int32_t)((n + PYLO_TILE_ELEMS - 1) / PYLO_TILE_ELEMS);
+  w.sums = SUMS_STRIDE;
+  w.wfold = PYLO_WFOLD_STRIDE;
+  w.tile_part = (int64_t)w.n_tiles * PYLO_STAT_STRIDE;
+  *out = w;
+  return 0;
+}
+
+int64_t pylo_b200_workspace_bytes(const pylo_ws_layout* w, int tensor_part, int unit_part) {
+  if (!w) return -1;
+  auto pad = [](int64_t floats) { return (floats + 63) / 64 * 64 * 4; };
+  int64_t bytes = 0;
+  if (tensor_part)
+    bytes += pad(w->f_a) + pad(w->f_b) + pad(w->sum_a) + pad(w->sum_b) + pad(w->fx) + pad(w->part_a) + pad(w->part_b) +
+             pad(w->h_a) + pad(w->h_b) + pad(w->closed);
+  if (unit_part) bytes += pad(w->sums) + pad(w->wfold) + pad(w->tile_part);
+  return bytes;
+}
 
 int pylo_b200_grad_sumsq(const pylo_gvec* descs, const pylo_tile* tiles, int n_tiles, float* scratch,
                          float* out, void* stream) {
@@ -1629,7 +1675,6 @@ int pylo_b200_grad_sumsq(const pylo_gvec* descs, const pylo_tile* tiles, int n_t
 // ------------------------------------------------------------------------------------------------
 static __device__ __align__(256) float g_static_sumsq_scratch[PYLO_STATIC_SCRATCH_TILES];
 
-#define PYLO_MAX_DEVICES 64
 static float* g_static_scratch_addr[PYLO_MAX_DEVICES] = {nullptr};
 static std::mutex g_static_scratch_mutex;
 

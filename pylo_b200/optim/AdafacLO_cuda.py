@@ -115,6 +115,11 @@ class _AdafacFamily(Optimizer):
         for _, plan in self._plans.values():
             plan.check_status()
 
+    def clear_status(self):
+        """Acknowledge a reported tensor-core timeout so that the apply kernels store again."""
+        for _, plan in self._plans.values():
+            plan.clear_status()
+
     def _run_group(self, gi, group, plist, prm, lr, wd, exp_mult, step_mult, clip_norm, stream):
         sig = tuple(p.data_ptr() for p in plist)
         cached = self._plans.get(gi)
@@ -122,6 +127,7 @@ class _AdafacFamily(Optimizer):
             cached = (sig, self._build_plan(plist))
             self._plans[gi] = cached
         plan: LoPlan = cached[1]
+        plan._poll_status()  # refuse the step before any state (the step counters included) is advanced
         steps = []
         for p in plist:
             st = self.state[p]["step"]

@@ -197,11 +197,12 @@ class _Celo2Family(Optimizer):
             gnorm_ptr = total.data_ptr()
 
         for gi, group in enumerate(self.param_groups):
+            if self._shared_adam:
+                # every group advances on every step, with or without gradients (ELO_CELO2_cuda.py:215-216)
+                group["step"] = group.get("step", 0) + 1
             plist = [p for p in group["params"] if p.grad is not None]
             if not plist:
                 continue
-            if self._shared_adam:
-                group["step"] = group.get("step", 0) + 1
             sig = tuple((p.data_ptr(), bool(group["is_embedding"]), bool(group["use_adamw_for_1d"])) for p in plist)
             cached = self._plans.get(gi)
             if cached is None or cached[0] != sig:

@@ -209,6 +209,11 @@ class VeLO_CUDA(Optimizer):
             "rank": torch.stack([self.state[p]["rank_onehot"] for p in plist]).contiguous(),
             "loss": torch.zeros(1, **f32),
         }
+        # the nine time features are computed on the host (as the reference does) and cross through pinned staging
+        # buffers, two in turn, so that the copy never stalls the host
+        buf["frac_stage"] = [torch.zeros(9, dtype=torch.float32).pin_memory() for _ in range(2)]
+        buf["frac_event"] = [None, None]
+        buf["frac_turn"] = 0
         layers = [self.state[p]["layer_idx"] for p in plist]
         buf["layer_of"] = torch.tensor(layers, dtype=torch.int32, device=dev)
         tensors = []
@@ -277,7 +282,15 @@ class VeLO_CUDA(Optimizer):
         L.check(L.lib.pylo_b200_velo_loss_features(lb["means"].data_ptr(), lb["iteration"].data_ptr(),
                                                    lb["running_min"].data_ptr(), lb["decays"].data_ptr(),
                                                    buf["loss"].data_ptr(), buf["loss9"].data_ptr(), stream), "velo_loss_features")
-        buf["fraction9"].copy_(fractional_tanh_embed(fraction), non_blocking=True)
+        turn = buf["frac_turn"]
+        buf["frac_turn"] = turn ^ 1
+        if buf["frac_event"][turn] is not None:
+            buf["frac_event"][turn].synchronize()  # the copy issued two steps ago has long finished
+        buf["frac_stage"][turn].copy_(fractional_tanh_embed(fraction))
+        buf["fraction9"].copy_(buf["frac_stage"][turn], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        buf["frac_event"][turn] = ev
 
         prm = L.StepParams()
         prm.family, prm.nan_to_num, prm.wd_mode = L.FAM_VELO, 0, 3

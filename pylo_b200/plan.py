@@ -8,6 +8,7 @@ sequence of one step.  Nothing here touches tensor values on the host.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 import math
 from dataclasses import dataclass
@@ -162,6 +163,7 @@ class LoPlan:
         tdesc = np.zeros(T, dtype=L.DESC_DTYPE)
         ws_items = []  # (table, row, field, count)
         atiles, rtiles, generic = [], [], []
+        ws_bytes = 0  # the library's own count of the workspace, checked against the layout below
         for i, t in enumerate(tensors):
             shape = tuple(t.p.shape)
             n = t.p.numel()
@@ -205,21 +207,25 @@ class LoPlan:
                 fast = (O == 1 and M == 1 and I == 1 and Y % 4 == 0 and n < 2**31
                         and not (t.slice_last2 and t.p.dim() > 2) and _aligned16(t.p, t.m, t.v, t.out))
                 d["mode"] = L.MODE_FAST2D if fast else L.MODE_GENERIC
-                ws_items += [("t", i, "f_a", 3 * La), ("t", i, "f_b", 3 * Lb), ("t", i, "sum_a", La), ("t", i, "sum_b", Lb)]
+                # sub-buffer sizes and the phase-A tiling come from the library (pylo_b200_workspace_layout), so that
+                # this table and a table built by any other host of the C ABI agree
+                ws = L.workspace_layout(family, int(d["mode"]), n, La, Lb, X if fast else 0, Y if fast else 0)
+                ws_items += [("t", i, f, getattr(ws, f)) for f in ("f_a", "f_b", "sum_a", "sum_b")]
                 if fast:
-                    rb = min(128, max(32, ((X + 127) // 128 + 7) // 8 * 8))  # rows per strip
-                    n_strips = (X + rb - 1) // rb
-                    n_cb = (Y + L.A_COLS - 1) // L.A_COLS
-                    d["rb"], d["n_strips"], d["n_cb"] = rb, n_strips, n_cb
-                    ws_items += [("t", i, "fx", 4 * La), ("t", i, "part_a", X * n_cb), ("t", i, "part_b", n_strips * Y),
-                                 ("t", i, "h_a", La * H * 2), ("t", i, "h_b", Lb * H)]
-                    for s in range(n_strips):
-                        for cb in range(n_cb):
+                    d["rb"], d["n_strips"], d["n_cb"] = ws.rb, ws.n_strips, ws.n_cb
+                    assert ws.rb == min(128, max(32, ((X + 127) // 128 + 7) // 8 * 8)) and ws.h_a == La * H * 2
+                    ws_items += [("t", i, f, getattr(ws, f)) for f in ("fx", "part_a", "part_b", "h_a", "h_b")]
+                    for s in range(ws.n_strips):
+                        for cb in range(ws.n_cb):
                             atiles.append((i, s, cb, 0))
-                    rtiles += [(i, 0, cb, 0) for cb in range(n_cb)]
+                    rtiles += [(i, 0, cb, 0) for cb in range(ws.n_cb)]
                 else:
                     generic.append(i)
             ws_items.append(("t", i, "closed", L.STAT_STRIDE))
+            ws_bytes += L.lib.pylo_b200_workspace_bytes(
+                C.byref(L.workspace_layout(family, int(d["mode"]), n, int(d["La"]), int(d["Lb"]),
+                                           int(d["X"]) if d["mode"] == L.MODE_FAST2D else 0,
+                                           int(d["Y"]) if d["mode"] == L.MODE_FAST2D else 0)), 1, 0)
 
         # units of element-wise work
         self.sliced = any(t.slice_last2 and t.p.dim() > 2 for t in tensors)
@@ -243,20 +249,25 @@ class LoPlan:
                         if udesc[f][u]:
                             udesc[f][u] += 4 * off
                     ws_items.append(("u", u, "closed", L.STAT_STRIDE))  # stays zero: no closed forms for a slice
+                    ws_bytes += (L.STAT_STRIDE + 63) // 64 * 256
         else:
             udesc = tdesc
         sizes = [int(udesc["n"][u]) for u in range(U)]
         tiles, ranges = make_tiles(sizes)
         for u, (t0, k) in enumerate(ranges):
             udesc["tile0"][u], udesc["n_tiles"][u] = t0, k
-            ws_items += [("u", u, "sums", L.SUMS_STRIDE), ("u", u, "wfold", L.WFOLD_STRIDE),
-                         ("u", u, "tile_part", k * L.STAT_STRIDE)]
+            ws = L.workspace_layout(family, L.MODE_VEC1D, sizes[u])  # the per-unit part depends on the element count only
+            assert ws.n_tiles == k
+            ws_items += [("u", u, f, getattr(ws, f)) for f in ("sums", "wfold", "tile_part")]
+            ws_bytes += L.lib.pylo_b200_workspace_bytes(C.byref(ws), 0, 1)
         # workspace: every sub-buffer starts on a 256-byte boundary
         off = 0
         placed = []
         for table, row, fld, count in ws_items:
             placed.append((table, row, fld, off))
             off += (count + 63) // 64 * 64
+        if off * 4 != ws_bytes:
+            raise AssertionError(f"workspace layout ({off * 4} bytes) disagrees with pylo_b200_workspace_bytes ({ws_bytes})")
         self.workspace = torch.zeros(max(off, 64), dtype=torch.float32, device=self.device)
         base = self.workspace.data_ptr()
         for table, row, fld, o in placed:
@@ -295,6 +306,13 @@ class LoPlan:
                     ctiles.append((unit_of[i], rtile, ctile, tag))
         self.ctiles = DeviceTable(np.array(ctiles, dtype=np.int32).reshape(-1, 4).view(L.ATILE_DTYPE).reshape(-1), self.device)
         self.n_ctiles = len(ctiles)
+        #: the kernel that takes the FAST2D tensors' apply sweep (also the key of its timings in phase_times())
+        if self.tensor_cores:
+            self.apply_kernel = "k_apply_adafac_tc16" if self.tensor_cores == "fp16" else "k_apply_adafac_tc"
+        elif family == L.FAM_ADAFAC:
+            self.apply_kernel = "k_apply_adafac_cols"
+        else:
+            self.apply_kernel = "k_apply_packed<CELO2>" if family == L.FAM_CELO2 else "k_apply_packed<VELO>"
         #: device flag the tensor-core kernel raises when one of its bounded waits ran out
         self.status = torch.zeros(64, dtype=torch.int32, device=self.device) if self.tensor_cores else None
         # a pinned copy of the flag follows every launch without blocking; the next launch looks at it once it landed
@@ -338,9 +356,11 @@ class LoPlan:
             self.desc.upload()
 
     # ------------------------------------------------------------------ launch sequence
+    #: the kernel that dominates each timed phase, for reports
+    KERNEL_OF = {"rowcol_sums": "k_rowcol_fast", "factor_update": "k_factor_update", "state_moments": "k_state_moments",
+                 "finalize_moments": "k_finalize_moments", "prep_apply": "k_prep_apply"}
     #: kernels each C-ABI call launches (for the launch count the benchmark reports)
-    LAUNCHES = {"rowcol_sums": 1, "factor_update": 1, "state_moments": 1, "finalize_moments": 1,
-                "prep_apply": 1, "apply": 1, "apply_cols": 1}
+    LAUNCHES = {"rowcol_sums": 1, "factor_update": 1, "state_moments": 1, "finalize_moments": 1, "prep_apply": 1}
 
     def enable_profile(self, on: bool = True):
         """Record a CUDA-event pair around every phase launch (read back with :meth:`phase_times`)."""
@@ -356,13 +376,14 @@ class LoPlan:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
         L.check(fn(*args), name)
-        self.launch_count = getattr(self, "launch_count", 0) + self.LAUNCHES[name]
+        self.launch_count = getattr(self, "launch_count", 0) + self.LAUNCHES.get(name, 1)
         if prof is not None:
             b.record()
             prof.setdefault(name, []).append((a, b))
 
     def run_front(self, prm: L.StepParams, stream: int, reverse_b: bool = True):
         """Phases A, A2, B, B2."""
+        self._poll_status()  # before any state of this step is touched
         prm.step_delta = getattr(self, "step_delta", 0.0)
         pp = C.byref(prm)
         if self.n_atiles or self.n_generic:
@@ -374,32 +395,51 @@ class LoPlan:
                    int(reverse_b), pp, stream)
         self._call("finalize_moments", L.lib.pylo_b200_finalize_moments, self.desc.ptr, self.n_units, stream)
 
+    def _poll_status(self):
+        """Raise if the copy of the status word that followed an earlier tensor-core launch has landed non-zero."""
+        if self._status_event is not None and self._status_event.query() and int(self._status_host[0]) != 0:
+            raise L.PyloLibError("apply_adafac_tc: a wait on the tensor core timed out in an earlier step; the kernel "
+                                 "kept the old values of the parameters it could not finish, and launches write "
+                                 "nothing until clear_status() is called")
+
     def run_back(self, prm: L.StepParams, stream: int, reverse_c: bool = False):
         """Phases P, C."""
         prm.no_tables = int(bool(self.tensor_cores))
         pp = C.byref(prm)
         self._call("prep_apply", L.lib.pylo_b200_prep_apply, self.desc.ptr, self.n_units, pp, stream)
         if self.n_ctiles and self.tensor_cores:
-            if self._status_event is not None and self._status_event.query() and int(self._status_host[0]) != 0:
-                raise L.PyloLibError("apply_adafac_tc: a wait on the tensor core timed out in an earlier step; "
-                                     "the parameters written since are invalid")
+            self._poll_status()
             fn = L.lib.pylo_b200_apply_adafac_tc16 if self.tensor_cores == "fp16" else L.lib.pylo_b200_apply_adafac_tc
-            self._call("apply_cols", fn, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp, self.status.data_ptr(), stream)
-            if stream == current_stream_ptr():  # the watch copy is enqueued by torch on its current stream
+            self._call(self.apply_kernel, fn, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp, self.status.data_ptr(), stream)
+            # a pinned copy of the status word follows the launch on the launch's own stream, without blocking
+            ctx = (torch.cuda.stream(torch.cuda.ExternalStream(stream, device=self.device))
+                   if stream != current_stream_ptr() else contextlib.nullcontext())
+            with ctx:
                 self._status_host.copy_(self.status[:1], non_blocking=True)
                 self._status_event = torch.cuda.Event()
                 self._status_event.record()
         elif self.n_ctiles:
             fn = L.lib.pylo_b200_apply_adafac_cols if self.family == L.FAM_ADAFAC else L.lib.pylo_b200_apply_packed
-            self._call("apply_cols", fn, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp, stream)
+            self._call(self.apply_kernel, fn, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp, stream)
         if self.n_tiles_slow:
-            self._call("apply", L.lib.pylo_b200_apply, self.desc.ptr, self.tiles_slow.ptr, self.n_tiles_slow, int(reverse_c), pp, stream)
-
+            self._call("k_apply", L.lib.pylo_b200_apply, self.desc.ptr, self.tiles_slow.ptr, self.n_tiles_slow, int(reverse_c), pp, stream)
 
     def check_status(self):
-        """Synchronise and raise if the tensor-core kernel reported a wait that ran out (its results are invalid)."""
+        """Synchronise and raise if the tensor-core kernel reported a wait that ran out.
+
+        The kernel keeps the old value of every parameter it could not finish, so nothing invalid was written, but
+        the step is incomplete; until :meth:`clear_status` the kernel stores nothing at all.  Call this before a
+        checkpoint is written."""
         if self.status is not None and int(self.status[0].item()) != 0:
-            raise L.PyloLibError("apply_adafac_tc: a wait on the tensor core timed out; this step's parameters are invalid")
+            raise L.PyloLibError("apply_adafac_tc: a wait on the tensor core timed out; this step is incomplete "
+                                 "(unfinished parameters kept their old values)")
+
+    def clear_status(self):
+        """Acknowledge a reported timeout: the next launches store again."""
+        if self.status is not None:
+            self.status.zero_()
+            self._status_host.zero_()
+            self._status_event = None
 
 
 class GradNorm:

@@ -1,5 +1,8 @@
 """Drive the CUDA optimizer classes over a golden case's seeded inputs."""
 
+import json
+import os
+
 import torch
 
 import cases
@@ -74,3 +77,31 @@ def compare(traj_a, traj_b, init):
             worst_u = max(worst_u, float(torch.clamp(err - 4 * 1.2e-7 * b.abs(), min=0).max() / (mv + 1e-30)))
         res[t] = (worst_p, worst_u)
     return res
+
+
+def update_error(a, b, p0):
+    """Worst per-element relative error of the UPDATE ``p - p0`` of one tensor.
+
+    ``a`` is the tensor under test, ``b`` the reference, ``p0`` the value both started from.  The error of an
+    element is taken against max(|its reference update|, rms of the tensor's reference update), after four ulps
+    of the parameter itself are discounted (the update is read back as a difference of two fp32 parameters, which
+    carries that much rounding whatever the arithmetic that produced it).
+    """
+    a, b, p0 = a.double().reshape(-1), b.double().reshape(-1), p0.double().reshape(-1)
+    du = b - p0
+    err = torch.clamp((a - b).abs() - 4 * 1.2e-7 * b.abs(), min=0)
+    scale = torch.maximum(du.abs(), du.pow(2).mean().sqrt())
+    return float((err / (scale + 1e-30)).max())
+
+
+def compare_updates(traj_a, traj_b, init):
+    """{step: worst :func:`update_error` over the tensors} for two trajectories."""
+    return {t: max(update_error(a, b, p0) for a, b, p0 in zip(traj_a[t], traj_b[t], init)) for t in traj_b}
+
+
+def log_parity(test, **numbers):
+    """Append observed error figures to the file named by PYLO_PARITY_LOG (used when tolerances are reviewed)."""
+    path = os.environ.get("PYLO_PARITY_LOG")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps({"test": test, **{k: (v if isinstance(v, (int, float, str)) else repr(v)) for k, v in numbers.items()}}) + "\n")

@@ -1,0 +1,188 @@
+"""GPU parity against the CPU oracle at the sizes the benchmark runs at.
+
+The golden trajectories bind small tensors.  These tests bind the same classes, through the C ABI, where the
+benchmark configurations put them:
+
+* every family on ``(1024, 4096) + (4096,)`` (the benchmark's own CPU sample), three steps, 1e-5 per element;
+* CELO2 on ``(4096, 4096) + (4096,)`` with per-row log-normal gradients (mu = -7), weight decay 0.1,
+  Newton-Schulz on and off, two steps;
+* one 100-step trajectory per family on ``(256, 384) + (384,)``: 1e-5 after the first step, 1e-4 after the last;
+* the VeLO front end at its real width (``VeLORNN()`` with 512 hidden units, 256 weight banks) over 300 tensors:
+  ``lr_mult``, the mixed per-tensor network weights and the parameters.
+
+Bounds, all fp32: relative error per parameter element as above, the movement since initialisation within 1e-4
+of its largest entry, and the update of every element within ``UPDATE_TOL`` of max(|its update|, rms update).
+"""
+
+import pytest
+import torch
+
+import cases
+import cuda_util as CU
+
+pytestmark = pytest.mark.gpu
+
+REL_1STEP = 1e-5
+REL_END = 1e-4
+MOVE_TOL = 1e-4
+UPDATE_TOL = 1e-3
+
+FAMILIES = ["adafaclo", "elo", "celo2", "elo_celo2", "velo"]
+
+
+def _nets(family, lstm_hidden=512):
+    from pylo_b200 import models
+
+    torch.manual_seed(0)
+    if family in ("adafaclo", "elo"):
+        return models.MetaMLP(39, 32, 1)
+    if family in ("celo2", "elo_celo2"):
+        return models.CELO2MLP()
+    rnn, mlp = models.VeLORNN(lstm_hidden_size=lstm_hidden), models.VeLOMLP()
+    with torch.no_grad():
+        for name, p in mlp.named_parameters():
+            if name.endswith("_") or "_." in name:
+                p.mul_(0.05)  # the banks are N(0, 1) by default and are multiplied by 100 when mixed
+    return rnn, mlp
+
+
+# hyper-parameters of the benchmark's optimizers (bench.py: build_optimizer)
+HP = {
+    "adafaclo": dict(lr=1e-3, step_mult=0.01, exp_mult=0.001),
+    "elo": dict(lr=1e-3, weight_decay=0.1, clip_grad=True),
+    "celo2": dict(lr=1e-3, weight_decay=0.1),
+    "elo_celo2": dict(lr=1e-3, weight_decay=0.1),
+    "velo": dict(lr=1e-3, num_steps=10000),
+}
+# gradient scale and kind of the benchmark configuration each family is quoted on
+GRADS = {
+    "adafaclo": dict(grad_scale=1e-4), "elo": dict(grad_scale=1e-4),
+    "celo2": dict(grad_kind="rowlognormal", log_mu=-7.0), "elo_celo2": dict(grad_scale=1e-3),
+    "velo": dict(grad_scale=1e-3, grad_kind="outliers"),
+}
+
+
+def _make_pair(family, shapes, params, hp=None, nets=None):
+    """(CUDA optimizer over ``params``, oracle) with the same seeded meta-weights."""
+    from oracle import pylo_oracle as O
+    from pylo_b200 import optim
+
+    hp = dict(HP[family] if hp is None else hp)
+    net = nets if nets is not None else _nets(family)
+    if family in ("adafaclo", "elo"):
+        cls = optim.AdafacLO_CUDA if family == "adafaclo" else optim.ELO_CUDA
+        return cls(params, network=net, **hp), O.AdafacLOOracle(net.flat_weights(), elo=(family == "elo"), **hp)
+    if family in ("celo2", "elo_celo2"):
+        cls = optim.CELO2_CUDA if family == "celo2" else optim.ELO_CELO2_CUDA
+        okw = dict(hp)
+        if family == "elo_celo2":
+            okw = dict(dict(clip_grad=True, adam_lr_mult=20.0), **okw)  # the CUDA class's own defaults
+        return cls(params, network=net, **hp), O.CELO2Oracle(net.flat_weights(), shared_adam=(family == "elo_celo2"), **okw)
+    rnn, mlp = net
+    ora = O.VeLOOracle(O.rnn_weights_from_module(rnn), O.bank_from_module(mlp), shapes, **hp)
+    return optim.VeLO_CUDA(params, rnn=rnn, mlp=mlp, **hp), ora
+
+
+def _run_both(family, case, steps, record, hp=None, nets=None):
+    """Drive the CUDA class and the oracle over the case's seeded inputs; {step: [tensors]} for both."""
+    init = cases.init_values(case)
+    params = [torch.nn.Parameter(v.cuda()) for v in init]
+    ref = [v.clone() for v in init]
+    opt, ora = _make_pair(family, case["shapes"], params, hp, nets)
+    got, want = {}, {}
+    for t in range(1, steps + 1):
+        grads = cases.grads_at(case, t)
+        for p, g in zip(params, grads):
+            p.grad = g.cuda()
+        if family == "velo":
+            opt.step(torch.tensor(cases.velo_loss(t), dtype=torch.float32, device="cuda"))
+            ora.step(ref, grads, cases.velo_loss(t))
+        else:
+            opt.step()
+            ora.step(ref, grads)
+        if t in record:
+            got[t] = [p.detach().cpu().clone() for p in params]
+            want[t] = [r.clone() for r in ref]
+    if hasattr(opt, "check_status"):
+        opt.check_status()
+    return got, want, init, opt, ora
+
+
+def _assert_bounds(test, got, want, init, update_tol=UPDATE_TOL):
+    res = CU.compare(got, want, init)
+    upd = CU.compare_updates(got, want, init)
+    first, last = min(res), max(res)
+    CU.log_parity(test, rel_first=res[first][0], rel_last=res[last][0], move=max(r[1] for r in res.values()),
+                  update=max(upd.values()))
+    assert res[first][0] < REL_1STEP, res
+    assert res[last][0] < (REL_END if last > 3 else REL_1STEP), res
+    assert all(r[1] < MOVE_TOL for r in res.values()), res
+    assert all(u < update_tol for u in upd.values()), upd
+
+
+@pytest.mark.parametrize("family", FAMILIES)
+def test_bench_sample_matches_oracle(family):
+    """(1024, 4096) + (4096,): the matrix and the vector the benchmark's CPU leg is timed on."""
+    case = dict(shapes=[(1024, 4096), (4096,)], init_seed=1, init_scale=0.02, grad_seed=2, **GRADS[family])
+    got, want, init, _, _ = _run_both(family, case, 3, [1, 3])
+    _assert_bounds(f"bench_sample[{family}]", got, want, init)
+
+
+@pytest.mark.parametrize("orthogonalize", [False, True])
+def test_celo2_4096_config_matches_oracle(orthogonalize):
+    """CELO2 on one 4096 x 4096 weight + a 4096 bias, per-row log-normal gradients (mu = -7, sigma = 1),
+    weight decay 0.1, Newton-Schulz on and off (its fifteen 4096^3 products run on the CPU in the oracle)."""
+    case = dict(shapes=[(4096, 4096), (4096,)], init_seed=1, init_scale=0.02, grad_seed=2, grad_kind="rowlognormal",
+                log_mu=-7.0)
+    hp = dict(lr=1e-3, weight_decay=0.1, orthogonalize=orthogonalize)
+    got, want, init, _, _ = _run_both("celo2", case, 2, [1, 2], hp=hp)
+    _assert_bounds(f"celo2_4096[orth={int(orthogonalize)}]", got, want, init)
+
+
+@pytest.mark.parametrize("family", FAMILIES)
+def test_hundred_step_trajectory_matches_oracle(family):
+    """100 steps with fresh seeded gradients each step: 1e-5 after the first, 1e-4 after the hundredth."""
+    case = dict(shapes=[(256, 384), (384,)], init_seed=3, init_scale=0.02, grad_seed=4, **GRADS[family])
+    nets = _nets(family, lstm_hidden=512)
+    got, want, init, _, _ = _run_both(family, case, 100, [1, 10, 100], nets=nets)
+    _assert_bounds(f"trajectory100[{family}]", got, want, init)
+
+
+def test_velo_front_end_at_full_width():
+    """``VeLORNN()`` as the benchmark builds it (512 hidden units, 2048 gates over 1024 inputs, 256 banks) over 300
+    tensors: the per-tensor step-size multipliers, the 159 mixed network weights of every tensor and the
+    parameters, after each of two steps (the second one runs on the LSTM state the first one left)."""
+    base = [(24, 16), (16,), (8, 40), (40,), (3, 4, 5), (1,), (12, 12), (5, 7)]
+    shapes = [base[i % len(base)] for i in range(300)]
+    case = dict(shapes=shapes, init_seed=7, init_scale=0.02, grad_seed=8, grad_scale=1e-3, grad_kind="outliers")
+    init = cases.init_values(case)
+    params = [torch.nn.Parameter(v.cuda()) for v in init]
+    ref = [v.clone() for v in init]
+    hp = dict(lr=1.0, num_steps=200, weight_decay=0.01)
+    opt, ora = _make_pair("velo", shapes, params, hp)
+    assert opt._H == 512 and opt._B == 256
+    T = len(shapes)
+    for t in (1, 2):
+        grads = cases.grads_at(case, t)
+        for p, g in zip(params, grads):
+            p.grad = g.cuda()
+        opt.step(torch.tensor(cases.velo_loss(t), dtype=torch.float32, device="cuda"))
+        ora.step(ref, grads, cases.velo_loss(t))
+        buf = opt._plan[1]["buf"]
+        lr_mult = buf["lr_mult"].cpu().double()
+        want_lr = torch.flip(ora.lr_mult, [0]).double()
+        e_lr = float((lr_mult - want_lr).abs().max() / want_lr.abs().max())
+        w = buf["weights"][:, :159].cpu().double()
+        want_w = torch.stack([st["mlp_weights"] for st in ora.state]).double()
+        e_w = float(((w - want_w).abs().max(dim=1).values / want_w.abs().max(dim=1).values).max())
+        h_gpu = opt.lstm_hidden_state[0].cpu().double()
+        e_h = float((h_gpu - ora.lstm_hidden_state[0].double()).abs().max())
+        CU.log_parity(f"velo_front_end[step={t}]", lr_mult=e_lr, weights=e_w, hidden=e_h, T=T)
+        assert e_lr < 2e-5, (t, e_lr)
+        assert e_w < 5e-5, (t, e_w)
+        assert e_h < 1e-5, (t, e_h)
+    got = {2: [p.detach().cpu() for p in params]}
+    res = CU.compare(got, {2: ref}, init)
+    upd = CU.compare_updates(got, {2: ref}, init)
+    CU.log_parity("velo_front_end[params]", rel=res[2][0], move=res[2][1], update=upd[2])
+    assert res[2][0] < REL_1STEP and res[2][1] < 1e-3, res

@@ -2,8 +2,9 @@
 
 Tolerances, all fp32: 1e-5 relative per parameter element after one step and
 1e-4 after the full trajectory (up to 100 steps); in addition the *movement*
-of the parameters since initialisation must agree to 2e-3 of its largest
-entry, which is the sharper test when the learning rate is small.
+of the parameters since initialisation must agree to 1e-4 of its largest
+entry, and the update of every single element to 1e-3 of max(|its update|, rms
+update of its tensor): the sharper tests when the learning rate is small.
 """
 
 import pytest
@@ -17,7 +18,8 @@ pytestmark = pytest.mark.gpu
 
 REL_1STEP = 1e-5
 REL_END = 1e-4
-MOVE_TOL = 2e-3
+MOVE_TOL = 1e-4
+UPDATE_TOL = 1e-3
 
 LO_CASES = sorted(G.CASES)
 
@@ -29,10 +31,14 @@ def test_cuda_matches_oracle(name):
     ref = G.run(case, G.make_oracle(case, weights, variant="cuda"))
     got, _, _ = CU.run_cuda(case, weights)
     res = CU.compare(got, ref, cases.init_values(case))
+    upd = CU.compare_updates(got, ref, cases.init_values(case))
     first, last = min(res), max(res)
+    CU.log_parity(f"golden[{name}]", rel_first=res[first][0], rel_last=res[last][0], move=max(r[1] for r in res.values()),
+                  update=max(upd.values()))
     assert res[first][0] < REL_1STEP, res
     assert res[last][0] < REL_END, res
     assert all(r[1] < MOVE_TOL for r in res.values()), res
+    assert all(u < UPDATE_TOL for u in upd.values()), upd
 
 
 @pytest.mark.parametrize("name", [n for n in LO_CASES if n.startswith(("celo2_ref", "elo_celo2_ref", "celo2_single"))])

@@ -3,7 +3,7 @@
 
 The two hidden layers run as tcgen05 products with every operand split into a high and a low part (TF32, or
 fp16 with normalised features); the results must stay inside the same bounds as the scalar-FMA path: 1e-5 relative per element after one
-step, 1e-4 after the whole trajectory, movement within 2e-3 of its largest entry against the oracle, and
+step, 1e-4 after the whole trajectory, movement within 1e-4 of its largest entry against the oracle, and
 within 1e-5 of the movement against the scalar-FMA path of the library itself at the full 4096 x 4096 size.
 """
 
@@ -17,6 +17,7 @@ import golden_util as G
 pytestmark = pytest.mark.gpu
 
 PRECISIONS = ["3xtf32", "2xfp16"]
+MOVE_TOL = 1e-4
 ADAFAC_CASES = sorted(n for n, c in G.CASES.items() if c["family"] in ("adafaclo", "elo"))
 
 
@@ -48,7 +49,7 @@ def test_tensor_core_path_matches_oracle(name, prec):
     first, last = min(res), max(res)
     assert res[first][0] < 1e-5, res
     assert res[last][0] < 1e-4, res
-    assert all(r[1] < 2e-3 for r in res.values()), res
+    assert all(r[1] < MOVE_TOL for r in res.values()), res
 
 
 @pytest.mark.parametrize("name", ADAFAC_CASES)
@@ -61,7 +62,7 @@ def test_scalar_fma_path_matches_oracle(name):
     assert not any(plan.tensor_cores for _, plan in opt._plans.values())
     res = CU.compare(got, ref, cases.init_values(case))
     first, last = min(res), max(res)
-    assert res[first][0] < 1e-5 and res[last][0] < 1e-4 and all(r[1] < 2e-3 for r in res.values()), res
+    assert res[first][0] < 1e-5 and res[last][0] < 1e-4 and all(r[1] < MOVE_TOL for r in res.values()), res
 
 
 # two-dimensional shapes that are factored (both sides >= 32) with ragged edges: columns that do not fill a
@@ -92,7 +93,8 @@ def test_tensor_core_ragged_shapes_match_oracle(family, prec):
         ora.step(ref, grads)
     opt.check_status()
     res = CU.compare({3: [p.detach().cpu() for p in params]}, {3: ref}, init)
-    assert res[3][0] < 1e-5 and res[3][1] < 2e-3, res
+    CU.log_parity(f"tc_ragged[{family},{prec}]", rel=res[3][0], move=res[3][1])
+    assert res[3][0] < 1e-5 and res[3][1] < MOVE_TOL, res
 
 
 @pytest.mark.parametrize("prec", PRECISIONS)
@@ -144,14 +146,17 @@ def test_unknown_mlp_precision_is_rejected():
         _make("adafaclo", [p], mlp_precision="bf16")
 
 
-def test_timed_out_wait_is_reported_by_a_later_step():
-    """The kernel ORs 1 into a device flag when one of its bounded waits runs out.  Here the flag is set from the
-    host (no GPU misbehaviour involved): check_status() must raise, and so must a later step on its own."""
+@pytest.mark.parametrize("prec", PRECISIONS)
+def test_reported_timeout_keeps_parameters_and_is_raised(prec):
+    """The kernel ORs 1 into a device word when one of its bounded waits runs out, and a launch that finds the
+    word set stores nothing.  Here the word is set from the host (no GPU misbehaviour involved): the launch must
+    leave the parameters exactly as they were, check_status() must raise, a later step must raise by itself
+    before it touches any state, and clear_status() must bring the optimizer back."""
     from pylo_b200 import _lib as L
 
     gen = torch.Generator(device="cuda").manual_seed(3)
     p = torch.nn.Parameter(torch.randn(256, 256, device="cuda", generator=gen) * 0.02)
-    opt = _make("adafaclo", [p], mlp_precision="3xtf32")
+    opt = _make("adafaclo", [p], mlp_precision=prec)
     p.grad = torch.randn(256, 256, device="cuda", generator=gen) * 1e-3
     opt.step()
     opt.check_status()
@@ -159,7 +164,16 @@ def test_timed_out_wait_is_reported_by_a_later_step():
     plan.status[0] = 1
     with pytest.raises(L.PyloLibError):
         opt.check_status()
-    opt.step()                 # this launch is followed by a copy of the flag to pinned memory
+    before = p.detach().clone()
+    opt.step()                 # this launch finds the word set; a copy of the word to pinned memory follows it
     torch.cuda.synchronize()
+    assert torch.equal(p.detach(), before), "a launch that found the status word set must not write parameters"
+    m_before = opt.state[p]["exp_avg"].clone()
     with pytest.raises(L.PyloLibError):
-        opt.step()             # ... which the next launch looks at
+        opt.step()             # ... which this step looks at before its first kernel
+    torch.cuda.synchronize()
+    assert torch.equal(opt.state[p]["exp_avg"], m_before), "the refused step must not have touched the state"
+    opt.clear_status()
+    opt.step()
+    opt.check_status()
+    assert not torch.equal(p.detach(), before)

@@ -75,3 +75,41 @@ def test_static_scratch_variant_refuses_what_does_not_fit():
     assert rc == L.ERR_STATIC_SCRATCH_TOO_SMALL
     with pytest.raises(L.PyloLibError, match="built-in scratch"):
         L.check(rc, "grad_sumsq_static")
+
+
+def test_static_scratch_variant_allocates_nothing():
+    """After the set-up call (which looks up the built-in array's address) a call on tables that already exist
+    must leave the device's free memory and torch's allocator counters exactly where they were."""
+    from pylo_b200 import _lib as L
+
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev).manual_seed(12)
+    grads = [torch.randn(n, generator=gen, device=dev) for n in SIZES[:4]]
+    items, tiles, n_tiles = _tables(grads, dev)
+    out = torch.zeros(1, dtype=torch.float32, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    L.check(L.lib.pylo_b200_grad_sumsq_static(items.ptr, tiles.ptr, n_tiles, out.data_ptr(), stream), "set-up call")
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info(dev)
+    alloc0, reserved0 = torch.cuda.memory_allocated(dev), torch.cuda.memory_reserved(dev)
+    for _ in range(3):
+        L.check(L.lib.pylo_b200_grad_sumsq_static(items.ptr, tiles.ptr, n_tiles, out.data_ptr(), stream), "grad_sumsq_static")
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info(dev)
+    assert (torch.cuda.memory_allocated(dev), torch.cuda.memory_reserved(dev)) == (alloc0, reserved0)
+    assert free1 == free0, "the allocation-free entry point changed the device's free memory"
+    assert float(out.item()) == pytest.approx(float(sum(g.double().pow(2).sum() for g in grads)), rel=1e-5)
+
+
+def test_static_scratch_variant_on_a_second_device():
+    """The built-in array exists once per GPU and its address is looked up per device: repeat the comparison on
+    cuda:1 where there is one."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("one GPU visible")
+    dev = torch.device("cuda", 1)
+    with torch.cuda.device(dev):
+        gen = torch.Generator(device=dev).manual_seed(13)
+        grads = [torch.randn(n, generator=gen, device=dev) * 2.0 for n in SIZES[:4]]
+        ref, got = _both(grads, dev)
+        assert got == pytest.approx(ref, rel=1e-6)
+        assert got == pytest.approx(float(sum(g.double().pow(2).sum() for g in grads)), rel=1e-5)
