@@ -49,7 +49,7 @@ B_BYTES = 40  # state_moments sweep: reads g, p, m(3), v; writes m(3), v
 # from ncu captures of a 4096 x 4096 case, not measured in this run; traffic grows in proportion to the elements
 NCU_TRAFFIC_PER_ELEM = {"k_apply_adafac_cols": 27.58, "k_apply_adafac_tc": 27.44}
 # TF32 / fp16 multiply-adds the tensor-core apply kernels issue per parameter (products x N x K, M = the element)
-TC_ISSUED_FMA_PER_PARAM = {"3xtf32": 25 * 32 * 8, "2xfp16": 13 * 32 * 16}
+TC_ISSUED_FMA_PER_PARAM = {"3xtf32": (3 * 64 + 3 * 32 + 4 * 64 + 4 * 32 + 32) * 8}
 
 
 def parse(argv=None):
@@ -64,9 +64,9 @@ def parse(argv=None):
     ap.add_argument("--no-orthogonalize", action="store_true", help="celo2 family: skip Newton-Schulz")
     ap.add_argument("--ns-precision", default="fp32", choices=["fp32", "3xtf32"],
                     help="celo2 family: Newton-Schulz products in fp32 (reference arithmetic) or as three TF32 tensor-core GEMMs")
-    ap.add_argument("--mlp-precision", default="3xtf32", choices=["fp32", "3xtf32", "2xfp16"],
+    ap.add_argument("--mlp-precision", default="3xtf32", choices=["fp32", "3xtf32"],
                     help="adafaclo / elo: the network's hidden layers as scalar fp32 FMAs, or as tensor-core products of "
-                         "operands split into two TF32 or two fp16 parts (fp32-faithful: three products per layer)")
+                         "operands split into two TF32 parts (fp32-faithful: hi x hi + hi x lo + lo x hi)")
     ap.add_argument("--blocks", type=int, default=8, help="N>1: stages whose parameter all-gathers overlap the next stage")
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "staged"],
                     help="N>1: how updated parameters reach the other ranks (peer stores fused into the apply kernels, "
@@ -506,11 +506,11 @@ def measure(args, dev, world, rank, local, headline):
                      "achieved": owned_n * STEP_BYTES[args.optimizer] / (ms_per_step * 1e-3) / 1e9,
                      "frac": owned_n * STEP_BYTES[args.optimizer] / (ms_per_step * 1e-3) / 1e9 / peak},
         }
-        if args.optimizer in ("adafaclo", "elo") and dominant in ("k_apply_adafac_tc", "k_apply_adafac_tc16"):
+        if args.optimizer in ("adafaclo", "elo") and dominant == "k_apply_adafac_tc":
             per_param = TC_ISSUED_FMA_PER_PARAM[args.mlp_precision]
             issued = per_launch_elems * per_param * 2 / (phase_ms[dominant] * 1e-3)
             roofline["tensor"] = {"network_fma_per_param": 1600, "issued_fma_per_param": per_param,
-                                  "operands": "tf32" if args.mlp_precision == "3xtf32" else "fp16",
+                                  "operands": "tf32", "products_per_128_params": 15,
                                   "issued_tflops": issued / 1e12,
                                   "network_fp32_equiv_tflops": per_launch_elems * 3200 / (phase_ms[dominant] * 1e-3) / 1e12}
         elif args.optimizer in ("adafaclo", "elo") and dominant in ("k_apply", "k_apply_adafac_cols") and clocks and clocks.get("sm_mhz"):

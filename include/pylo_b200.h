@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define PYLO_B200_ABI_VERSION 7
+#define PYLO_B200_ABI_VERSION 8
 
 /* optimizer families (which feature set / network geometry a launch uses) */
 #define PYLO_FAM_ADAFAC 0 /* AdafacLO_CUDA, ELO_CUDA: 28+11 features, 39-32-32-2 */
@@ -141,8 +141,8 @@ typedef struct pylo_step_params {
   float eps_feat;         /* inside rsqrt(v + eps): 1e-6 AdafacLO/ELO/VeLO, 1e-8 CELO2 */
   float eps_norm;         /* inside rsqrt(S/n + eps): 1e-5 AdafacLO/ELO/VeLO, 1e-9 CELO2 */
   float clip_val;         /* element-wise clamp of the gradient; +inf for none */
-  int32_t no_tables;      /* prep_apply: skip the per-row / per-column first-layer tables (the tensor-core apply
-                             kernel builds its operands from the factor vectors itself) */
+  int32_t no_tables;      /* prep_apply: 0 = make the per-row (desc.h_a) and per-column (desc.h_b) first-layer tables,
+                             1 = neither, 2 = the per-row table only (what the tensor-core apply kernel reads) */
   const float* gnorm_sq;  /* device scalar: sum of squares of all gradients, or NULL */
 } pylo_step_params;
 
@@ -258,22 +258,16 @@ int pylo_b200_apply_adafac_cols(const pylo_tensor_desc* descs, const pylo_atile*
 
 /* Phase C for the FAST2D tensors of the ADAFAC family on the tensor cores (no reference counterpart: the
  * reference evaluates the network with scalar FMAs, lo_kernel_apply learned_optimizer.cu:236-284).  Same inputs
- * and outputs as pylo_b200_apply_adafac_cols; the two hidden layers run as tcgen05 TF32 products with every
- * operand split into a high and a low TF32 part (three products per layer), which keeps a 32-term dot product
- * within ~3e-7 of the sum of its terms' magnitudes; non-finite features give NaN where the scalar path may give
- * an infinity.  ttiles: strip = row-strip index, cb = block of 128 columns, pad_ = rows per work item (one
- * warpgroup of a CTA takes a whole item).  status: device int the kernel ORs 1 into if a wait on the tensor core ran out (results are then
- * invalid); may be NULL. */
+ * and outputs as pylo_b200_apply_adafac_cols, except that of the two first-layer tables it reads only desc.h_a
+ * (run pylo_b200_prep_apply with no_tables = 2 or 0).  The two hidden layers run as tcgen05 TF32 products with
+ * every operand split into a high and a low TF32 part (hi x hi + hi x lo + lo x hi), which keeps a 32-term dot
+ * product within ~3e-7 of the sum of its terms' magnitudes; non-finite features give NaN where the scalar path may
+ * give an infinity.  ttiles: strip = row-strip index, cb = block of 128 columns, pad_ = rows per work item (one
+ * warpgroup of a CTA takes a whole item).  status: device int; the kernel ORs 1 into it if a wait on the tensor
+ * core ran out (the parameters it could not finish then keep their old values), and a launch that finds it
+ * non-zero stores nothing; may be NULL. */
 int pylo_b200_apply_adafac_tc(const pylo_tensor_desc* descs, const pylo_atile* ttiles, int n_ttiles,
                               const pylo_step_params* prm, int* status, void* stream);
-
-/* The same with fp16 operands: every operand split into an fp16 high and an fp16 low part, products as
- * kind::f16 (K = 16 per instruction, half the products and half the operand columns of the TF32 variant).  The
- * features enter the products normalised (their rsqrt(mean f^2 + eps) is applied to the feature, not folded into
- * the weights), which bounds them by sqrt(n) < 65504; conversions saturate.  Arguments as pylo_b200_apply_adafac_tc;
- * one warpgroup of a CTA (six per SM) takes a whole item. */
-int pylo_b200_apply_adafac_tc16(const pylo_tensor_desc* descs, const pylo_atile* ttiles, int n_ttiles,
-                                const pylo_step_params* prm, int* status, void* stream);
 
 /* Phase C for the FAST2D tensors of the CELO2 and VELO families (same arithmetic as pylo_b200_apply, done on
  * pairs of adjacent elements with packed fp32x2 instructions).  ctiles: strip = row-tile index, cb = column-tile

@@ -16,7 +16,7 @@ SUMS_STRIDE = 48
 TILE_ELEMS = 16384
 A_COLS = 1024
 WFOLD_STRIDE = 2432
-ABI_VERSION = 7
+ABI_VERSION = 8
 
 FAM_ADAFAC, FAM_CELO2, FAM_VELO = 0, 1, 2
 MODE_FAST2D, MODE_GENERIC, MODE_VEC1D = 0, 1, 2
@@ -104,7 +104,6 @@ def _load():
         "pylo_b200_apply": [vp, vp, i32, i32, C.POINTER(StepParams), vp],
         "pylo_b200_apply_adafac_cols": [vp, vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_apply_adafac_tc": [vp, vp, i32, C.POINTER(StepParams), vp, vp],
-        "pylo_b200_apply_adafac_tc16": [vp, vp, i32, C.POINTER(StepParams), vp, vp],
         "pylo_b200_apply_packed": [vp, vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_celo2_post_sums": [vp, vp, i32, vp],
         "pylo_b200_celo2_post_apply": [vp, vp, i32, vp],
@@ -127,7 +126,7 @@ def _load():
 lib, EXPORTED = _load()
 
 
-TC_WORKERS = {"tf32": 148 * 5, "fp16": 148 * 6}  # warpgroups a tensor-core apply kernel runs at once (5 or 6 per SM)
+TC_WORKERS = 148 * 4  # warpgroups the tensor-core apply kernel runs at once (four per SM)
 STATIC_SCRATCH_TILES = 65536
 ERR_STATIC_SCRATCH_TOO_SMALL = -4
 

@@ -9,7 +9,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_PATH = os.path.join(CSRC, "libpylo_b200.so")
 SOURCES = [os.path.join(CSRC, "pylo_kernels.cu")]
-HEADERS = [os.path.join(CSRC, "pylo_common.cuh"), os.path.join(CSRC, "pylo_apply_tc.cuh"), os.path.join(CSRC, "pylo_apply_tc16.cuh"), os.path.join(INCLUDE, "pylo_b200.h")]
+HEADERS = [os.path.join(CSRC, "pylo_common.cuh"), os.path.join(CSRC, "pylo_apply_tc.cuh"), os.path.join(INCLUDE, "pylo_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -37,7 +37,10 @@ def build(force=False, verbose=False):
     nvcc = find_nvcc()
     if nvcc is None:
         raise RuntimeError("nvcc not found: cannot build pylo_b200/csrc/libpylo_b200.so")
-    cmd = [nvcc] + NVCC_FLAGS + ["-I", INCLUDE, "-I", CSRC, "-o", LIB_PATH] + SOURCES
+    # PYLO_B200_NVCC_FLAGS: extra nvcc flags for a one-off build (e.g. -DTC_STAGE_CLOCKS for the stage clocks of the
+    # tensor-core apply kernel)
+    extra = os.environ.get("PYLO_B200_NVCC_FLAGS", "").split()
+    cmd = [nvcc] + NVCC_FLAGS + extra + ["-I", INCLUDE, "-I", CSRC, "-o", LIB_PATH] + SOURCES
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     res = subprocess.run(cmd, capture_output=True, text=True)

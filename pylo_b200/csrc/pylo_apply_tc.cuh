@@ -1,43 +1,50 @@
-// Phase C for AdafacLO / ELO on FAST2D tensors, tensor-core variant (included by pylo_kernels.cu).
+// Phase C for AdafacLO / ELO on FAST2D tensors on the tensor cores (included by pylo_kernels.cu).
 //
 // The per-element network is a pair of small dense products, [elements x 29] x [29 x 32] and
-// [elements x 32] x [32 x 32]; on the CUDA cores they cost ~1600 fp32 FMAs per element and bound
-// the whole step.  Here a warpgroup (128 threads) treats 128 consecutive elements of one tensor
-// row as the M = 128 rows of a tcgen05 TF32 product:
-//   * each thread builds its element's 16 element-wise features in registers and writes them with
-//     tcgen05.st into tensor memory, where they are operand A (lane = element, column = feature);
-//   * the twelve features that depend only on the row or only on the column join operand A as
-//     further columns (their split is made once per row by a few threads and once per work item
-//     per column), the first-layer bias rides on a constant-1 column, and the second-layer bias
-//     on one more small product against a constant operand;
-//   * fp32 accuracy is kept by splitting every operand into a TF32 high part and a TF32 low part
-//     and issuing three products per layer (lo x hi, hi x lo, hi x hi): the error of a 32-term dot
-//     product is ~3e-7 of the sum of its terms' magnitudes, against ~1.5e-7 for an fp32 FMA chain;
-//   * the weights (operand B) sit in shared memory in the K-major no-swizzle core-matrix layout,
-//     split the same way, rebuilt only when the CTA moves to another tensor;
-//   * relu, the split of the hidden activations, the two output heads and the parameter update
-//     stay on the CUDA cores, which work on one warpgroup's tile while the tensor core works on
-//     another's: five warpgroups per CTA, one CTA per SM; every warpgroup is an independent worker
-//     with its own work items, its own copy of the weights in shared memory, its own accumulator
-//     columns and its own barriers, so the warpgroups drift apart instead of marching in step.
+// [elements x 32] x [32 x 32]; on the CUDA cores they cost ~1600 fp32 FMAs per element and bound the whole
+// step.  Here a warpgroup (128 threads) treats 128 consecutive elements of one tensor row as the M = 128 rows
+// of tcgen05 TF32 products:
+//   * each thread builds its element's 16 element-wise features in registers and writes them with tcgen05.st
+//     into tensor memory, where they are operand A (lane = element, column = feature);
+//   * the six features that depend only on the element's column join operand A as six more columns, kept in
+//     registers for all rows of a work item; the six that depend only on its ROW are the same for all 128
+//     elements of the tile, so together with the first-layer bias they are a per-row bias vector: it is read from
+//     the table k_prep_apply makes (desc.h_a, 32 floats per row) and enters the product through operand B, as two
+//     rows (its high and low part) that meet two constant-1 columns of operand A.  First layer: K = 24;
+//   * fp32 accuracy is kept by splitting every operand into a TF32 high part and a TF32 low part.  Of the three
+//     products per layer that this needs (hi x hi, hi x lo, lo x hi) the two that share operand A run as ONE
+//     product of twice the width: operand B holds [B_hi | B_lo] stacked along N (N = 64), so the accumulator has
+//     64 columns, hi x hi in the first 32 and hi x lo in the last 32, and A_lo x B_hi accumulates into the first
+//     32.  The two halves are added when the accumulator is read back.  An instruction of width 64 costs the tensor
+//     pipe the same issue slot as one of width 32, so a tile takes 6 + 9 = 15 products instead of 25;
+//   * the second-layer bias is one more product, of a constant operand A (ones, in shared memory) with a block of
+//     operand B that holds the bias's high and low parts;
+//   * relu, the split of the hidden activations, the two output heads and the parameter update stay on the CUDA
+//     cores, which work on one warpgroup's tile while the tensor core works on another's: four warpgroups per
+//     CTA, one CTA per SM; every warpgroup is an independent worker with its own work items, its own copy of the
+//     weights in shared memory, its own 128 tensor-memory columns (64 operand A + 64 accumulator) and its own
+//     barriers, so the warpgroups drift apart instead of marching in step.
 // Every wait on the tensor core is bounded.  A thread whose wait ran out records it in *status, stops waiting
 // and stops storing (its parameters, and their copies on the peers, keep their old values), and goes on to
 // the end, where the kernel frees its tensor memory.  A launch that finds *status already set stores nothing.
 #pragma once
 
-#ifndef TC_WGS
-#define TC_WGS 5                 // warpgroups per CTA: 5 x 96 tensor-memory columns + 8 shared ones fit the SM's 512
-#endif
+#define TC_WGS 4                 // warpgroups per CTA: 4 x 128 tensor-memory columns are the SM's 512
 #define TC_NT (TC_WGS * 128)
+#ifndef TC_BOUND_THREADS
+#define TC_BOUND_THREADS TC_NT   // a larger bound lowers the register cap (65536 / bound): room for a co-resident kernel
+#endif
 #define TC_COLS 128              // tensor columns per work item: one per lane of the accumulator tile
-#define TC_WG_TMEM 96            // tensor-memory columns per warpgroup: [0,64) operand A, [64,96) accumulator
-#define TC_CONST_COL 480         // columns [480,488): the constant operand (1, 1, 0 ...) shared by all warpgroups
+#define TC_WG_TMEM 128           // tensor-memory columns per warpgroup: [0,64) operand A, [64,128) accumulator
+#define TC_K1 24                 // first-layer K: 16 element-wise + 6 column features + 2 constant columns
 #define TC_SPIN_LIMIT (1 << 20)
 #ifndef TC_POLL_SLEEP_NS
 #define TC_POLL_SLEEP_NS 40
 #endif
-#define TC_LBO 512               // bytes between 16-byte K chunks of operand B (32 rows x 16 bytes)
-#define TC_SBO 128               // bytes between groups of eight rows of operand B
+#define TC_LBO 512               // bytes between 16-byte K chunks of a 32-row operand B (32 rows x 16 bytes)
+#define TC_LBO64 1024            // the same for a 64-row (stacked) operand B
+#define TC_SBO 128               // bytes between groups of eight rows
+#define TC_ONES_BYTES 2304       // constant operand A: every 16-byte chunk is (1, 1, 0, 0)
 
 __device__ __forceinline__ void tc_alloc(uint32_t* dst_smem, int ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(dst_smem)), "r"(ncols) : "memory");
@@ -53,12 +60,19 @@ __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sy
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void wg_barrier(int wg) { asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory"); }
 
-// D[128 x 32] (+)= A[128 x 8] * B[32 x 8]^T, A in tensor memory, B through a shared-memory descriptor
+// D[128 x N] (+)= A[128 x 8] * B[N x 8]^T, A in tensor memory, B through a shared-memory descriptor
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// the same with A through a shared-memory descriptor
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
@@ -79,12 +93,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
-// 16 consecutive 32-bit columns of this thread's lane
+// 16 / 8 consecutive 32-bit columns of this thread's lane
 __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
 }
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -94,16 +112,20 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr) : "memory");
 }
 
-// float index of B[n][k] in the K-major no-swizzle layout: 8 x 16-byte core matrices, K chunks TC_LBO apart
-__host__ __device__ constexpr int tc_b_index(int n, int k) { return ((k >> 2) * TC_LBO + (n >> 3) * TC_SBO + (n & 7) * 16 + (k & 3) * 4) / 4; }
+// float index of B[n][k] in the K-major no-swizzle layout (8-row x 16-byte core matrices, K chunks `lbo` bytes apart)
+__host__ __device__ constexpr int tc_b_index(int n, int k, int lbo = TC_LBO) {
+  return ((k >> 2) * lbo + (n >> 3) * TC_SBO + (n & 7) * 16 + (k & 3) * 4) / 4;
+}
 
 // shared-memory matrix descriptor: start address, leading (K) and stride (row-group) byte offsets in 16-byte
 // units, descriptor version 1, no swizzle
-__device__ __forceinline__ uint64_t tc_desc(uint32_t saddr) {
-  return (uint64_t)((saddr >> 4) & 0x3fff) | ((uint64_t)(TC_LBO >> 4) << 16) | ((uint64_t)(TC_SBO >> 4) << 32) | ((uint64_t)1 << 46);
+__device__ __forceinline__ uint64_t tc_desc(uint32_t saddr, int lbo = TC_LBO, int sbo = TC_SBO) {
+  return (uint64_t)((saddr >> 4) & 0x3fff) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | ((uint64_t)1 << 46);
 }
-// instruction descriptor: fp32 accumulate, TF32 x TF32, both operands K-major, N = 32, M = 128
-constexpr uint32_t TC_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((32u >> 3) << 17) | ((128u >> 4) << 24);
+// instruction descriptor: fp32 accumulate, TF32 x TF32, both operands K-major, M = 128, N = 32 or 64
+constexpr uint32_t tc_idesc(uint32_t n) { return (1u << 4) | (2u << 7) | (2u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
+constexpr uint32_t TC_IDESC = tc_idesc(32);
+constexpr uint32_t TC_IDESC64 = tc_idesc(64);
 
 // read-only 128-bit load issued where it is written (the compiler would otherwise sink it to its first use)
 __device__ __forceinline__ float4 ldg4_early(const float* p) {
@@ -112,55 +134,38 @@ __device__ __forceinline__ float4 ldg4_early(const float* p) {
   return v;
 }
 
+// Stage clocks (debug builds with -DTC_STAGE_CLOCKS only): lane 0 of every warpgroup's first warp adds the cycles it
+// spends in each stage of a tile to status[8 + 12 * wg + stage].
+#ifdef TC_STAGE_CLOCKS
+#define TC_CLK_DECL long long clk_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long clk_t = clock64();
+#define TC_CLK(stage) { const long long now_ = clock64(); clk_acc[stage] += now_ - clk_t; clk_t = now_; }
+#define TC_CLK_FLUSH if (col == 0 && status) { for (int q_ = 0; q_ < 12; ++q_) atomicAdd(status + 8 + 12 * wg + q_, (int)(clk_acc[q_] >> 10)); }
+#else
+#define TC_CLK_DECL
+#define TC_CLK(stage)
+#define TC_CLK_FLUSH
+#endif
+
 __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
 
-// per-item constants; they are read back from shared memory at their points of use (volatile, so that the
-// compiler does not hoist them into registers for the whole row loop: at 512 threads a thread has 128 registers)
-struct TcItem {
-  const float* g;
-  float* p;
-  const float* m;
-  const float* v;
-  const float* fx;
-  const float* fac_a;
-  float* const* peer;
-  long long n;
-  float exp_mult, step_mult, wd, lr, lr_eff, gs;
-  int wd_mode, n_peer;
-};
-
-// One warpgroup's private shared memory: its copy of the weights, the vector features of its item's columns and
-// of its row in flight, its item constants and its tensor-core barrier.  Warpgroups never wait on one another.
-struct TcWgSmem {
-  float b1hi[32 * 32], b1lo[32 * 32];            // first layer: N = 32, K = 32 (28 features, bias row, 3 zero rows)
-  float b2hi[32 * 32], b2lo[32 * 32];            // second layer: N = 32, K = 32
-  float b2bias[32 * 8];                          // second-layer bias as a K = 8 block: (high part, low part, 0 ...)
-  float w3[64 + 4];                              // output layer, pair-major (Fold::W3P), then its two biases
-  float4 colf[3][TC_COLS];                       // the item's columns: 6 vector features, high parts then low parts
-  float4 rowf[2][4];                             // double-buffered: the same for the row in flight / the next, then the
-                                                 // row's three factors of the element-wise factored features
-  TcItem item;
+// One warpgroup's private shared memory: its copy of the weights and its tensor-core barrier.  Warpgroups never
+// wait on one another.
+struct __align__(128) TcWgSmem {
+  float b1[64 * TC_K1];   // first layer, rows 0..31 the high parts, 32..63 the low parts; K = 24 (K rows 22 and 23 of
+                          // the high half are rewritten for every tensor row: the row's bias vector, high and low part)
+  float b2[64 * 32];      // second layer, stacked the same way; K = 32
+  float b2bias[32 * 8];   // second-layer bias as a K = 8 block: (high part, low part, 0 ...)
+  float w3[64 + 4];       // output layer, pair-major (Fold::W3P), then its two biases
   uint64_t bar;
 };
 struct TcSmem {
   TcWgSmem wg[TC_WGS];
+  __align__(128) float ones[TC_ONES_BYTES / 4];
   uint32_t tmem_base;
   int poisoned;  // the status word at launch: non-zero means an earlier launch reported a timed-out wait
 };
 
-// the six vector features of one index of the "a" or "b" vector, feature j of 6: fac[j] (j < 3) or rsqrt(fac[j-3] + 1e-8)
-__device__ __forceinline__ float tc_vec_feature(const float* __restrict__ fac, int64_t len, int64_t i, int j) {
-  const float r = fac[(int64_t)(j % 3) * len + i];
-  return j < 3 ? r : rsqrtf(r + 1e-8f);
-}
-// slot of feature j (0..5) in the three float4 of high and low parts
-__device__ __forceinline__ void tc_put6(float4* q, int j, float v) {
-  const float hi = tf32_hi(v);
-  reinterpret_cast<float*>(q)[j] = hi;
-  reinterpret_cast<float*>(q)[6 + j] = v - hi;
-}
-
-__global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_desc* __restrict__ descs,
+__global__ void __launch_bounds__(TC_BOUND_THREADS, 1) k_apply_adafac_tc(const pylo_tensor_desc* __restrict__ descs,
                                                               const pylo_atile* __restrict__ ttiles, int n_ttiles,
                                                               const pylo_step_params prm, int* __restrict__ status) {
   using F = Fam<PYLO_FAM_ADAFAC>;
@@ -171,8 +176,10 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
   TcWgSmem& sm = smem.wg[wg];
   if (col == 0) mbar_init(&sm.bar, 1);
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  for (int e = tid; e < TC_ONES_BYTES / 4; e += TC_NT) smem.ones[e] = (e & 3) < 2 ? 1.0f : 0.0f;
   if (tid == 32) smem.poisoned = status ? *reinterpret_cast<volatile int*>(status) : 0;
   if (warp == 0) { tc_alloc(&smem.tmem_base, 512); tc_relinquish(); }
+  fence_async_smem();  // the constant operand is read by the tensor core through the async proxy
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -182,20 +189,13 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
   const uint32_t t_wg = smem.tmem_base + wg * TC_WG_TMEM;               // lane 0 of this warpgroup's columns
   const uint32_t t_lane = t_wg + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes
   const uint32_t tA = t_lane, tD = t_lane + 64;
-  if (wg == 0) {  // the constant operand (1, 1, 0 ...) that adds the second-layer bias as one more product
-    uint32_t one[8] = {0x3f800000u, 0x3f800000u, 0u, 0u, 0u, 0u, 0u, 0u};
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 ::"r"(smem.tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + TC_CONST_COL), "r"(one[0]), "r"(one[1]), "r"(one[2]),
-                   "r"(one[3]), "r"(one[4]), "r"(one[5]), "r"(one[6]), "r"(one[7]) : "memory");
-    tc_wait_st();
-  }
-  tc_fence_before();
-  __syncthreads();  // every warpgroup's products may read the constant operand
-  tc_fence_after();
-  constexpr uint64_t KSTEP = (2 * TC_LBO) >> 4;  // one product consumes two K chunks
+  constexpr uint64_t KSTEP64 = (2 * TC_LBO64) >> 4;  // one product consumes two K chunks of the stacked operand
+  // every row of the constant operand is (1, 1, 0, 0, ...): any in-range chunk of the buffer holds that pattern
+  const uint64_t desc_ones = tc_desc(smem_addr(smem.ones), 128, 128);
   uint32_t parity = 0;
   bool timed_out = false;
   int loaded = -1;
+  TC_CLK_DECL
   // every warpgroup is a worker of its own: it takes every (gridDim.x * TC_WGS)-th work item
   for (int t = blockIdx.x * TC_WGS + wg; t < n_items; t += gridDim.x * TC_WGS) {
     const pylo_atile ct = ttiles[t];
@@ -206,31 +206,27 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
     const bool colok = y < Y;
     const int yc = colok ? y : 0;
     const int x0 = ct.strip * rows_item;
-    wg_barrier(wg);  // the four warps are done with the previous item's column terms and weights
+    wg_barrier(wg);  // the four warps are done with the previous item's weights
     if (loaded != ct.tensor) {
-      // K order of the first layer: 16 element-wise features (0..12, 25..27), the six features of the row vector,
-      // the six of the column vector, the bias (against a constant 1), three zero rows
-      const int ka = d.r_is_a ? F::R : F::C, kra = d.r_is_a ? F::RR : F::RC;
+      // K order of the first layer: 16 element-wise features (0..12, 25..27), the six features of the column
+      // vector, then the two rows that carry the tensor row's bias vector (written per row below)
       const int kb = d.r_is_a ? F::C : F::R, krb = d.r_is_a ? F::RC : F::RR;
-      for (int e = col; e < 32 * 32; e += 128) {
+      for (int e = col; e < 32 * TC_K1; e += 128) {
         const int n = e & 31, kk = e >> 5;
         float w = 0.f;
         if (kk < 13) w = d.wfold[L::W1 + kk * 32 + n];
         else if (kk < 16) w = d.wfold[L::W1 + (kk + 12) * 32 + n];
-        else if (kk < 19) w = d.wfold[L::W1 + (ka + kk - 16) * 32 + n];
-        else if (kk < 22) w = d.wfold[L::W1 + (kra + kk - 19) * 32 + n];
-        else if (kk < 25) w = d.wfold[L::W1 + (kb + kk - 22) * 32 + n];
-        else if (kk < 28) w = d.wfold[L::W1 + (krb + kk - 25) * 32 + n];
-        else if (kk == 28) w = d.wfold[L::B1 + n];
+        else if (kk < 19) w = d.wfold[L::W1 + (kb + kk - 16) * 32 + n];
+        else if (kk < 22) w = d.wfold[L::W1 + (krb + kk - 19) * 32 + n];
         const float hi = tf32_hi(w);
-        sm.b1hi[tc_b_index(n, kk)] = hi;
-        sm.b1lo[tc_b_index(n, kk)] = w - hi;
+        sm.b1[tc_b_index(n, kk, TC_LBO64)] = hi;
+        sm.b1[tc_b_index(32 + n, kk, TC_LBO64)] = w - hi;
       }
       for (int e = col; e < 32 * 32; e += 128) {
         const int n = e & 31, k = e >> 5;
         const float w = d.wfold[L::W2 + k * 32 + n], hi = tf32_hi(w);
-        sm.b2hi[tc_b_index(n, k)] = hi;
-        sm.b2lo[tc_b_index(n, k)] = w - hi;
+        sm.b2[tc_b_index(n, k, TC_LBO64)] = hi;
+        sm.b2[tc_b_index(32 + n, k, TC_LBO64)] = w - hi;
       }
       for (int e = col; e < 32 * 8; e += 128) {
         const int n = e & 31, k = e >> 5;
@@ -241,63 +237,73 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
       if (col < 2) sm.w3[64 + col] = d.wfold[L::B3 + col];
       loaded = ct.tensor;
     }
-    for (int e = col; e < 6 * TC_COLS; e += 128) {
-      const int j = e / TC_COLS, c = e % TC_COLS, yy = ct.cb * TC_COLS + c;
-      const float v = yy < Y ? tc_vec_feature(d.fac_b, Y, yy, j) : 0.f;
+    // per-item constants: in registers for all rows of the item
+    const float* __restrict__ gp = d.g;
+    float* __restrict__ pp = d.p;
+    const float* __restrict__ mp = d.m;
+    const float* __restrict__ vp = d.v;
+    const float* __restrict__ fxp = d.fx;    // [X][4]: the row's three factors of the element-wise factored features
+    const float* __restrict__ hap = d.h_a;   // [X][32]: the row's first-layer bias vector (row features + bias)
+    const int64_t n = d.n;
+    const Peers peers = load_peers(d);
+    const float gs = grad_scale_of(d, prm);
+    const Fin fin{d.exp_mult, d.step_mult, d.wd, d.lr, d.wfold[L::SC + 1], 1.0f, prm.wd_mode};
+    // no clipping, no nan_to_num, no global-norm scale (AdafacLO's defaults): the gradient is used as it is
+    const bool plain_grad = !prm.nan_to_num && prm.clip_val == CUDART_INF_F && gs == 1.0f;
+    const float fb0 = d.f_b[yc], fb1 = d.f_b[Y + yc], fb2 = d.f_b[2 * (int64_t)Y + yc];
+    // the six features of this thread's column, high parts (then two ones) and low parts (then two zeros)
+    uint32_t chi[8], clo[8];
+#pragma unroll
+    for (int j = 0; j < 6; ++j) {
+      const float r = colok ? d.fac_b[(int64_t)(j % 3) * Y + yc] : 0.f;
+      const float v = colok ? (j < 3 ? r : rsqrtf(r + 1e-8f)) : 0.f;
       const float hi = tf32_hi(v);
-      reinterpret_cast<float*>(&sm.colf[j >> 2][c])[j & 3] = hi;
-      reinterpret_cast<float*>(&sm.colf[(6 + j) >> 2][c])[(6 + j) & 3] = v - hi;
+      chi[j] = __float_as_uint(hi);
+      clo[j] = __float_as_uint(v - hi);
     }
-    if (col < 6 && x0 < X) tc_put6(&sm.rowf[0][0], col, tc_vec_feature(d.fac_a, X, x0, col));
-    if (col >= 6 && col < 9 && x0 < X) reinterpret_cast<float*>(&sm.rowf[0][3])[col - 6] = d.fx[(int64_t)x0 * 4 + (col - 6)];
-    if (col == 0) {
-      TcItem& it = sm.item;
-      it.g = d.g; it.p = d.p; it.m = d.m; it.v = d.v; it.fx = d.fx; it.fac_a = d.fac_a;
-      it.peer = d.p_peer; it.n_peer = d.n_peer; it.n = d.n;
-      it.exp_mult = d.exp_mult; it.step_mult = d.step_mult; it.wd = d.wd; it.lr = d.lr;
-      it.lr_eff = d.wfold[L::SC + 1]; it.gs = grad_scale_of(d, prm); it.wd_mode = prm.wd_mode;
-    }
+    chi[6] = chi[7] = 0x3f800000u;
+    clo[6] = clo[7] = 0u;
     fence_async_smem();  // the tensor core reads the weights through the async proxy
     wg_barrier(wg);
-    const float fb0 = d.f_b[yc], fb1 = d.f_b[Y + yc], fb2 = d.f_b[2 * (int64_t)Y + yc];
-    const volatile TcItem& ic = sm.item;
-    // no clipping, no nan_to_num, no global-norm scale (AdafacLO's defaults): the gradient is used as it is
-    const bool plain_grad = !prm.nan_to_num && prm.clip_val == CUDART_INF_F && ic.gs == 1.0f;
     float cg, cp, cm0, cm1, cm2, cv;
-    auto load_row = [&](int x, float& g, float& p, float& m0, float& m1, float& m2, float& v) {
+    float4 cfa;
+    float hrow = 0.f;  // lanes 0..31 of the warpgroup's first warp: entry `col` of the row's bias vector
+    auto load_row = [&](int x, float& g, float& p, float& m0, float& m1, float& m2, float& v, float4& fa, float& hr) {
+      const int xc = x < X ? x : 0;
       const int64_t idx = (colok && x < X) ? (int64_t)x * Y + y : 0;
-      const int64_t n = ic.n;
-      const float* mp = ic.m;
-      g = ldg_early(ic.g + idx); p = ldg_early(ic.p + idx); m0 = ldg_early(mp + idx);
-      m1 = ldg_early(mp + n + idx); m2 = ldg_early(mp + 2 * n + idx); v = ldg_early(ic.v + idx);
+      g = ldg_early(gp + idx); p = ldg_early(pp + idx); m0 = ldg_early(mp + idx);
+      m1 = ldg_early(mp + n + idx); m2 = ldg_early(mp + 2 * n + idx); v = ldg_early(vp + idx);
+      fa = ldg4_early(fxp + 4 * (int64_t)xc);
+      if (col < 32) hr = ldg_early(hap + (int64_t)xc * 32 + col);
     };
-    load_row(x0, cg, cp, cm0, cm1, cm2, cv);
-    // threads 0..8 carry one row-wide value for the row after next: the row vector's factor (0..5) or one of the
-    // row's three factors (6..8); one global load each, consumed an iteration later, so that its latency never sits
-    // between two barriers
-    auto load_fac = [&](int x) {
-      const float* src = ic.fac_a;
-      int64_t off = 0;
-      if (x < X) {
-        if (col < 6) off = (int64_t)(col % 3) * X + x;
-        else if (col < 9) { src = ic.fx; off = (int64_t)x * 4 + (col - 6); }
-      }
-      return ldg_early(src + off);
-    };
-    float fac_next = load_fac(x0 + 1);
+    load_row(x0, cg, cp, cm0, cm1, cm2, cv, cfa, hrow);
+    TC_CLK(7)  // item set-up
 #pragma unroll 1
     for (int i = 0; i < rows_item; ++i) {
       const int x = x0 + i;  // the same for the whole warpgroup
       if (x >= X) break;
-      // the next row's row-wide values, for the next iteration (two warpgroup barriers lie in between)
-      if (col < 6) tc_put6(&sm.rowf[(i + 1) & 1][0], col, col < 3 ? fac_next : rsqrtf(fac_next + 1e-8f));
-      else if (col < 9) reinterpret_cast<float*>(&sm.rowf[(i + 1) & 1][3])[col - 6] = fac_next;
-      fac_next = load_fac(x + 2);
+#ifdef TC_LOADS_AT_TOP
+      // the next row's operands: requested a whole row ahead of their use
+      float ng, np_, nm0, nm1, nm2, nv, nhrow = 0.f;
+      float4 nfa;
+      load_row(x + 1, ng, np_, nm0, nm1, nm2, nv, nfa, nhrow);
+#endif
+      TC_CLK(8)  // next row's loads issued
+      // ---- the row's bias vector into operand B (the previous row's first-layer products are complete)
+#ifndef TC_NO_HROW
+      if (col < 32) {
+        const float hi = tf32_hi(hrow);
+        *reinterpret_cast<float2*>(&sm.b1[tc_b_index(col, 22, TC_LBO64)]) = make_float2(hi, hrow - hi);
+#ifndef TC_NO_ROW_FENCE
+        fence_async_smem();
+#endif
+      }
+#endif
+      TC_CLK(9)  // bias vector written
       // ---- operand A of the first layer, high and low parts
       {
-        const float g = plain_grad ? cg : xform_grad(cg, ic.gs, prm.clip_val, prm.nan_to_num);
+        const float g = plain_grad ? cg : xform_grad(cg, gs, prm.clip_val, prm.nan_to_num);
         const float rs = rsqrt_pos(cv + prm.eps_feat);
-        const float4 cfa = sm.rowf[i & 1][3];
         const float k0 = cfa.x * fb0, k1 = cfa.y * fb1, k2 = cfa.z * fb2;
         const float fe[16] = {g, cp, cm0, cm1, cm2, cv, cm0 * rs, cm1 * rs, cm2 * rs, rs,
                               k0 * g, k1 * g, k2 * g, k0 * cm0, k1 * cm1, k2 * cm2};
@@ -308,102 +314,108 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
           hi[k] = __float_as_uint(h);
           lo[k] = __float_as_uint(fe[k] - h);
         }
+        TC_CLK(10)  // features and split
         tc_st16(tA, hi);
-        tc_st16(tA + 32, lo);
-        const float4 r0 = sm.rowf[i & 1][0], r1 = sm.rowf[i & 1][1], r2 = sm.rowf[i & 1][2];
-        const float4 c0 = sm.colf[0][col], c1 = sm.colf[1][col], c2 = sm.colf[2][col];
-        // (r0, r1.xy) = row high parts, (r1.zw, r2) = row low parts; the same for the column
-        const uint32_t vhi[16] = {__float_as_uint(r0.x), __float_as_uint(r0.y), __float_as_uint(r0.z), __float_as_uint(r0.w),
-                                  __float_as_uint(r1.x), __float_as_uint(r1.y), __float_as_uint(c0.x), __float_as_uint(c0.y),
-                                  __float_as_uint(c0.z), __float_as_uint(c0.w), __float_as_uint(c1.x), __float_as_uint(c1.y),
-                                  0x3f800000u, 0u, 0u, 0u};
-        const uint32_t vlo[16] = {__float_as_uint(r1.z), __float_as_uint(r1.w), __float_as_uint(r2.x), __float_as_uint(r2.y),
-                                  __float_as_uint(r2.z), __float_as_uint(r2.w), __float_as_uint(c1.z), __float_as_uint(c1.w),
-                                  __float_as_uint(c2.x), __float_as_uint(c2.y), __float_as_uint(c2.z), __float_as_uint(c2.w),
-                                  0u, 0u, 0u, 0u};
-        tc_st16(tA + 16, vhi);
-        tc_st16(tA + 48, vlo);
+        tc_st8(tA + 16, chi);
+        tc_st16(tA + 24, lo);
+        tc_st8(tA + 40, clo);
       }
+#ifndef TC_LOADS_AT_TOP
       // the next row's operands: requested now that this row's are consumed (only p is still needed, for the
       // update), so the two sets never share the register file; they land during the two products
       float np_;
-      load_row(x + 1, cg, np_, cm0, cm1, cm2, cv);
+      load_row(x + 1, cg, np_, cm0, cm1, cm2, cv, cfa, hrow);
+#endif
+      TC_CLK(0)  // features, split, stores issued
       tc_wait_st();
       tc_fence_before();
       wg_barrier(wg);
+      TC_CLK(1)  // wait for the stores + warpgroup barrier
       if (col == 0) {
         tc_fence_after();
-        const uint64_t desc_b1hi = tc_desc(smem_addr(sm.b1hi)), desc_b1lo = tc_desc(smem_addr(sm.b1lo));
+        const uint64_t desc_b1 = tc_desc(smem_addr(sm.b1), TC_LBO64);
 #pragma unroll
-        for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 32 + 8 * s, desc_b1hi + s * KSTEP, TC_IDESC, s > 0);  // lo x hi
+        for (int s = 0; s < 3; ++s) tc_mma(t_wg + 64, t_wg + 8 * s, desc_b1 + s * KSTEP64, TC_IDESC64, s > 0);   // hi x [hi | lo]
 #pragma unroll
-        for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 8 * s, desc_b1lo + s * KSTEP, TC_IDESC, 1);           // hi x lo
-#pragma unroll
-        for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 8 * s, desc_b1hi + s * KSTEP, TC_IDESC, 1);           // hi x hi
+        for (int s = 0; s < 3; ++s) tc_mma(t_wg + 64, t_wg + 24 + 8 * s, desc_b1 + s * KSTEP64, TC_IDESC, 1);    // lo x hi
         tc_commit(&sm.bar);
       }
       __syncwarp();
       if (!timed_out && !mbar_wait(&sm.bar, parity)) timed_out = true;
       parity ^= 1;
       tc_fence_after();
-      // ---- hidden layer 1: relu, split, back into tensor memory as operand A of the second layer
+      TC_CLK(2)  // first-layer products: issue + wait
+      // ---- hidden layer 1: add the accumulator's halves, relu, split, back into tensor memory as operand A
       {
-        uint32_t dv0[16], dv1[16];
-        tc_ld16(tD, dv0);       // both halves are requested before the first is touched: one load latency, not two
-        tc_ld16(tD + 16, dv1);
+        uint32_t d0[16], d1[16], e0[16], e1[16];
+        tc_ld16(tD, d0);        // everything is requested before anything is touched: one load latency
+        tc_ld16(tD + 32, d1);
+        tc_ld16(tD + 16, e0);
+        tc_ld16(tD + 48, e1);
         tc_wait_ld();
-        auto split_store = [&](const uint32_t (&dv)[16], int half) {
+        TC_CLK(3)  // accumulator read-back
+        auto split_store = [&](const uint32_t (&a)[16], const uint32_t (&b)[16], int half) {
           uint32_t hi[16], lo[16];
 #pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            const float h = fmaxf(__uint_as_float(dv[k]), 0.f), hh = tf32_hi(h);
-            hi[k] = __float_as_uint(hh);
-            lo[k] = __float_as_uint(h - hh);
+          for (int k = 0; k < 16; k += 2) {
+            float s0, s1;
+            unpack2(add2(pack2(__uint_as_float(a[k]), __uint_as_float(a[k + 1])), pack2(__uint_as_float(b[k]), __uint_as_float(b[k + 1]))), s0, s1);
+            s0 = fmaxf(s0, 0.f); s1 = fmaxf(s1, 0.f);
+            const float h0 = tf32_hi(s0), h1 = tf32_hi(s1);
+            hi[k] = __float_as_uint(h0); hi[k + 1] = __float_as_uint(h1);
+            lo[k] = __float_as_uint(s0 - h0); lo[k + 1] = __float_as_uint(s1 - h1);
           }
           tc_st16(tA + 16 * half, hi);
           tc_st16(tA + 32 + 16 * half, lo);
         };
-        split_store(dv0, 0);
-        split_store(dv1, 1);
+        split_store(d0, d1, 0);
+        split_store(e0, e1, 1);
       }
+      TC_CLK(4)  // relu, split, stores issued
       tc_wait_st();
       tc_fence_before();
       wg_barrier(wg);
+      TC_CLK(1)
       if (col == 0) {
         tc_fence_after();
-        const uint64_t desc_b2hi = tc_desc(smem_addr(sm.b2hi)), desc_b2lo = tc_desc(smem_addr(sm.b2lo));
+        const uint64_t desc_b2 = tc_desc(smem_addr(sm.b2), TC_LBO64);
         const uint64_t desc_b2bias = tc_desc(smem_addr(sm.b2bias));
-        tc_mma(t_wg + 64, smem.tmem_base + TC_CONST_COL, desc_b2bias, TC_IDESC, 0);                                // bias
 #pragma unroll
-        for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 32 + 8 * s, desc_b2hi + s * KSTEP, TC_IDESC, 1);      // lo x hi
+        for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 8 * s, desc_b2 + s * KSTEP64, TC_IDESC64, s > 0);   // hi x [hi | lo]
 #pragma unroll
-        for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 8 * s, desc_b2lo + s * KSTEP, TC_IDESC, 1);           // hi x lo
-#pragma unroll
-        for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 8 * s, desc_b2hi + s * KSTEP, TC_IDESC, 1);           // hi x hi
+        for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 32 + 8 * s, desc_b2 + s * KSTEP64, TC_IDESC, 1);    // lo x hi
+        tc_mma_ss(t_wg + 64, desc_ones, desc_b2bias, TC_IDESC, 1);                                               // bias
         tc_commit(&sm.bar);
       }
       __syncwarp();
       if (!timed_out && !mbar_wait(&sm.bar, parity)) timed_out = true;
       parity ^= 1;
       tc_fence_after();
-      // ---- hidden layer 2 (relu) and the two output heads as packed dot products over unit pairs
+      TC_CLK(5)  // second-layer products: issue + wait
+      // ---- hidden layer 2 (halves added, relu) and the two output heads as packed dot products over unit pairs
       uint64_t od[2] = {0ull, 0ull}, om[2] = {0ull, 0ull};
       {
-        uint32_t dv0[16], dv1[16];
-        tc_ld16(tD, dv0);
-        tc_ld16(tD + 16, dv1);
+        uint32_t d0[16], d1[16], e0[16], e1[16];
+        tc_ld16(tD, d0);
+        tc_ld16(tD + 32, d1);
+        tc_ld16(tD + 16, e0);
+        tc_ld16(tD + 48, e1);
         tc_wait_ld();
-        auto heads = [&](const uint32_t (&dv)[16], int half) {
+        TC_CLK(3)
+        auto heads = [&](const uint32_t (&a)[16], const uint32_t (&b)[16], int half) {
 #pragma unroll
           for (int jp = 0; jp < 8; ++jp) {
             const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(&sm.w3[4 * (half * 8 + jp)]);  // (dir pair, mag pair)
-            const uint64_t r = pack2(fmaxf(__uint_as_float(dv[2 * jp]), 0.f), fmaxf(__uint_as_float(dv[2 * jp + 1]), 0.f));
+            float s0, s1;
+            unpack2(add2(pack2(__uint_as_float(a[2 * jp]), __uint_as_float(a[2 * jp + 1])),
+                         pack2(__uint_as_float(b[2 * jp]), __uint_as_float(b[2 * jp + 1]))), s0, s1);
+            const uint64_t r = pack2(fmaxf(s0, 0.f), fmaxf(s1, 0.f));
             od[jp & 1] = fma2(w.x, r, od[jp & 1]);
             om[jp & 1] = fma2(w.y, r, om[jp & 1]);
           }
         };
-        heads(dv0, 0);
-        heads(dv1, 1);
+        heads(d0, d1, 0);
+        heads(e0, e1, 1);
       }
       {
         float a, b, c, dd;
@@ -411,16 +423,21 @@ __global__ void __launch_bounds__(TC_NT, 1) k_apply_adafac_tc(const pylo_tensor_
         unpack2(add2(om[0], om[1]), c, dd);
         const float o0 = (a + b) + sm.w3[64], o1 = (c + dd) + sm.w3[65];
         if (colok && !timed_out) {  // after a wait that ran out the accumulators are not to be trusted: keep the old value
-          const Fin fin{ic.exp_mult, ic.step_mult, ic.wd, ic.lr, ic.lr_eff, 1.0f, ic.wd_mode};
           const float pn = finish<PYLO_FAM_ADAFAC>(cp, o0, o1, fin);
           const int64_t idx = (int64_t)x * Y + y;
-          ic.p[idx] = pn;
-          peer_store(Peers{ic.peer, ic.n_peer}, idx, pn);
+          pp[idx] = pn;
+          peer_store(peers, idx, pn);
         }
       }
+#ifdef TC_LOADS_AT_TOP
+      cg = ng; cp = np_; cm0 = nm0; cm1 = nm1; cm2 = nm2; cv = nv; cfa = nfa; hrow = nhrow;
+#else
       cp = np_;
+#endif
+      TC_CLK(6)  // heads, update, store
     }
   }
+  TC_CLK_FLUSH
   if (timed_out && status) atomicOr(status, 1);
   tc_fence_before();
   __syncthreads();

@@ -565,7 +565,7 @@ __global__ void __launch_bounds__(NT) k_prep_apply(const pylo_tensor_desc* __res
       o[L::SC + 1] = d.lr_mult ? d.lr * d.lr_mult[0] : d.lr;
     }
   }
-  if (d.mode != PYLO_MODE_FAST2D || prm.no_tables) return;
+  if (d.mode != PYLO_MODE_FAST2D || prm.no_tables == 1) return;
   // first-layer contribution of the features that depend only on the "a" index (plus bias) / "b" index
   const int64_t La = d.X, Lb = d.Y;
   const int ka = d.r_is_a ? F::R : F::C, kra = d.r_is_a ? F::RR : F::RC;
@@ -583,6 +583,7 @@ __global__ void __launch_bounds__(NT) k_prep_apply(const pylo_tensor_desc* __res
     if (FAM == PYLO_FAM_ADAFAC) d.h_a[e] = acc;
     else { d.h_a[2 * e] = acc; d.h_a[2 * e + 1] = acc; }  // stored as (v, v) pairs for the packed kernel
   }
+  if (prm.no_tables == 2) return;  // the per-row table only
   for (int64_t e = (int64_t)slice * NT + tid; e < Lb * H; e += (int64_t)slices * NT) {
     const int64_t i = e / H;
     const int j = (int)(e % H);
@@ -1047,7 +1048,6 @@ __global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const 
 }
 
 #include "pylo_apply_tc.cuh"
-#include "pylo_apply_tc16.cuh"
 
 // ================================================================================================
 // Phase C for CELO2 / ELO_CELO2 / VeLO on FAST2D tensors: packed kernel.
@@ -1766,7 +1766,8 @@ int pylo_b200_prep_apply(const pylo_tensor_desc* descs, int n_tensors, const pyl
   CHECK_ARG(descs && prm && n_tensors >= 0);
   if (n_tensors == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
-  const dim3 grid(n_tensors, 8);
+  // the table loops stride over grid.y slices; with few tensors in a launch the slices are what fills the GPU
+  const dim3 grid(n_tensors, n_tensors >= 64 ? 8 : 48);
   switch (prm->family) {
     case PYLO_FAM_ADAFAC: k_prep_apply<PYLO_FAM_ADAFAC><<<grid, NT, 0, s>>>(descs, *prm); break;
     case PYLO_FAM_CELO2: k_prep_apply<PYLO_FAM_CELO2><<<grid, NT, 0, s>>>(descs, *prm); break;
@@ -1804,22 +1805,11 @@ int pylo_b200_apply_adafac_tc(const pylo_tensor_desc* descs, const pylo_atile* t
                               const pylo_step_params* prm, int* status, void* stream) {
   CHECK_ARG(descs && ttiles && prm && n_ttiles >= 0 && prm->family == PYLO_FAM_ADAFAC);
   if (n_ttiles == 0) return 0;
-  // more than half an SM's shared memory: one CTA per SM, which then owns all of the SM's tensor memory
+  // more than half an SM's shared memory is requested: one CTA per SM, which then owns all of the SM's tensor memory
   constexpr int smem = sizeof(TcSmem) > 120 * 1024 ? (int)sizeof(TcSmem) : 120 * 1024;
   static bool configured[PYLO_MAX_DEVICES] = {};
   if (int rc = allow_dynamic_smem(k_apply_adafac_tc, smem, configured)) return rc;
   k_apply_adafac_tc<<<grid_for(n_ttiles, 1), TC_NT, smem, (cudaStream_t)stream>>>(descs, ttiles, n_ttiles, *prm, status);
-  return launch_status();
-}
-
-int pylo_b200_apply_adafac_tc16(const pylo_tensor_desc* descs, const pylo_atile* ttiles, int n_ttiles,
-                                const pylo_step_params* prm, int* status, void* stream) {
-  CHECK_ARG(descs && ttiles && prm && n_ttiles >= 0 && prm->family == PYLO_FAM_ADAFAC);
-  if (n_ttiles == 0) return 0;
-  constexpr int smem = sizeof(ThSmem) > 120 * 1024 ? (int)sizeof(ThSmem) : 120 * 1024;  // one CTA per SM
-  static bool configured[PYLO_MAX_DEVICES] = {};
-  if (int rc = allow_dynamic_smem(k_apply_adafac_tc16, smem, configured)) return rc;
-  k_apply_adafac_tc16<<<grid_for(n_ttiles, 1), TH_NT, smem, (cudaStream_t)stream>>>(descs, ttiles, n_ttiles, *prm, status);
   return launch_status();
 }
 

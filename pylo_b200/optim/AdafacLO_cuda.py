@@ -57,8 +57,8 @@ class _AdafacFamily(Optimizer):
         self._w_flat = torch.cat([t.reshape(-1) for t in flat]).to(self.device).contiguous()
         self._plans = {}
         self._gnorm = None
-        if self.mlp_precision not in ("fp32", "3xtf32", "2xfp16"):
-            raise ValueError(f"mlp_precision must be 'fp32', '3xtf32' or '2xfp16', got {self.mlp_precision!r}")
+        if self.mlp_precision not in ("fp32", "3xtf32"):
+            raise ValueError(f"mlp_precision must be 'fp32' or '3xtf32', got {self.mlp_precision!r}")
         self.process_group = None   # set (or set _sharded) when the tensors of the model are split over ranks
         self._sharded = False
         self.after_group = None     # optional callable(group index), called once a param group's kernels are enqueued
@@ -108,7 +108,7 @@ class _AdafacFamily(Optimizer):
                 p=p.data, m=st["exp_avg"], v=st["exp_avg_sq"], fac_r=st["exp_avg_sq_r"], fac_c=st["exp_avg_sq_c"],
                 fdims=fd, rcm_axis=axis, w=self._w_flat, peer_ptrs=getattr(p, "_pylo_peer_ptrs", None),
                 peer_multicast=getattr(p, "_pylo_peer_multicast", False)))
-        return LoPlan(L.FAM_ADAFAC, tensors, self.device, tensor_cores={"fp32": False, "3xtf32": "tf32", "2xfp16": "fp16"}[self.mlp_precision])
+        return LoPlan(L.FAM_ADAFAC, tensors, self.device, tensor_cores=(self.mlp_precision == "3xtf32"))
 
     def check_status(self):
         """Synchronise and raise if a tensor-core launch of an earlier step reported a timed-out wait."""

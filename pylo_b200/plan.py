@@ -119,16 +119,16 @@ class DeviceTable:
 def apply_tile_shape(family: int, X: int, Y: int, tensor_cores=None):
     """(rows per work item, columns per work item, tag for ``pylo_atile.pad_``) of a FAST2D tensor's apply sweep.
 
-    * tensor-core kernels (AdafacLO family, ``tensor_cores`` = "tf32" / "fp16"): an item is rt rows x 128 columns,
-      taken by one warpgroup (5 or 6 per SM); as many rows as possible (the column terms are loaded once per item)
-      while the tensor still yields >= 8 items per warpgroup; tag = rt;
+    * tensor-core kernel (AdafacLO family, ``tensor_cores`` true): an item is rt rows x 128 columns, taken by one
+      warpgroup (four per SM); as many rows as possible (the column terms are loaded once per item) while the
+      tensor still yields >= 8 items per warpgroup; tag = rt;
     * AdafacLO family on the CUDA cores: n_sub sub-tiles of 32 rows in one block of 32..256 columns, as long as
       possible while the tensor still yields >= 8 items per SM; tag = columns | n_sub << 16;
     * CELO2 / VeLO: four columns per thread, tag = threads per row.
     """
     if tensor_cores:
         ncol = (Y + 127) // 128
-        rt = next((r for r in (64, 32, 16) if ((X + r - 1) // r) * ncol >= 8 * L.TC_WORKERS[tensor_cores]), 8)
+        rt = next((r for r in (64, 32, 16) if ((X + r - 1) // r) * ncol >= 8 * L.TC_WORKERS), 8)
         return rt, 128, rt
     if family == L.FAM_ADAFAC:
         cw = min((256, 128, 64, 32), key=lambda c: ((Y + c - 1) // c * c - Y, -c))
@@ -151,11 +151,8 @@ class LoPlan:
 
     def __init__(self, family: int, tensors: List[LoTensor], device, tensor_cores=False):
         self.family = family
-        # False, or the operand format of the tensor-core apply kernel: "tf32" (True means this) or "fp16"
-        kind = "tf32" if tensor_cores is True else (tensor_cores or None)
-        if kind not in (None, "tf32", "fp16"):
-            raise ValueError(f"tensor_cores must be False, 'tf32' or 'fp16', got {tensor_cores!r}")
-        self.tensor_cores = kind if family == L.FAM_ADAFAC else None
+        # whether the AdafacLO family's FAST2D tensors take the tensor-core apply kernel (TF32 operands)
+        self.tensor_cores = bool(tensor_cores) and family == L.FAM_ADAFAC
         self.tensors = tensors
         self.device = torch.device(device)
         T = len(tensors)
@@ -308,7 +305,7 @@ class LoPlan:
         self.n_ctiles = len(ctiles)
         #: the kernel that takes the FAST2D tensors' apply sweep (also the key of its timings in phase_times())
         if self.tensor_cores:
-            self.apply_kernel = "k_apply_adafac_tc16" if self.tensor_cores == "fp16" else "k_apply_adafac_tc"
+            self.apply_kernel = "k_apply_adafac_tc"
         elif family == L.FAM_ADAFAC:
             self.apply_kernel = "k_apply_adafac_cols"
         else:
@@ -404,13 +401,13 @@ class LoPlan:
 
     def run_back(self, prm: L.StepParams, stream: int, reverse_c: bool = False):
         """Phases P, C."""
-        prm.no_tables = int(bool(self.tensor_cores))
+        # the tensor-core kernel needs the per-row table only (2); the CUDA-core kernels need both (0)
+        prm.no_tables = 2 if self.tensor_cores else 0
         pp = C.byref(prm)
         self._call("prep_apply", L.lib.pylo_b200_prep_apply, self.desc.ptr, self.n_units, pp, stream)
         if self.n_ctiles and self.tensor_cores:
             self._poll_status()
-            fn = L.lib.pylo_b200_apply_adafac_tc16 if self.tensor_cores == "fp16" else L.lib.pylo_b200_apply_adafac_tc
-            self._call(self.apply_kernel, fn, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp, self.status.data_ptr(), stream)
+            self._call(self.apply_kernel, L.lib.pylo_b200_apply_adafac_tc, self.desc.ptr, self.ctiles.ptr, self.n_ctiles, pp, self.status.data_ptr(), stream)
             # a pinned copy of the status word follows the launch on the launch's own stream, without blocking
             ctx = (torch.cuda.stream(torch.cuda.ExternalStream(stream, device=self.device))
                    if stream != current_stream_ptr() else contextlib.nullcontext())

@@ -10,8 +10,17 @@ benchmark configurations put them:
 * the VeLO front end at its real width (``VeLORNN()`` with 512 hidden units, 256 weight banks) over 300 tensors:
   ``lr_mult``, the mixed per-tensor network weights and the parameters.
 
-Bounds, all fp32: relative error per parameter element as above, the movement since initialisation within 1e-4
-of its largest entry, and the update of every element within ``UPDATE_TOL`` of max(|its update|, rms update).
+Bounds, all fp32: relative error per parameter element as above, the movement since initialisation within
+``MOVE_TOL`` of its largest entry, and the update of every element within ``UPDATE_TOL`` of max(|its update|, rms
+update).
+
+Newton-Schulz on large, badly conditioned matrices is the one place where these bounds cannot hold between ANY two
+fp32 implementations: the iteration multiplies the small singular directions of its input by ~3.4 per round, so the
+rounding noise of the first product (which depends on the summation order of the GEMM) comes out ~500 times larger.
+The CPU oracle in fp32 is itself 1e-3 away from the same oracle in fp64 on the per-row log-normal gradients of the
+4096 x 4096 configuration.  Those cases are therefore anchored on the fp64 oracle: the CUDA result must be as close
+to it as the fp32 CPU oracle is (within a factor), and the raw step that enters Newton-Schulz must match the
+oracle's to the usual bound.
 """
 
 import pytest
@@ -24,8 +33,9 @@ pytestmark = pytest.mark.gpu
 
 REL_1STEP = 1e-5
 REL_END = 1e-4
-MOVE_TOL = 1e-4
-UPDATE_TOL = 1e-3
+MOVE_TOL = 2e-5     # observed: <= 4e-6 on every case below
+UPDATE_TOL = 1e-4   # observed: <= 1.6e-5
+NS_FACTOR = 3.0     # Newton-Schulz on large matrices: allowed distance to the fp64 oracle, in units of the fp32 oracle's
 
 FAMILIES = ["adafaclo", "elo", "celo2", "elo_celo2", "velo"]
 
@@ -83,7 +93,7 @@ def _make_pair(family, shapes, params, hp=None, nets=None):
     return optim.VeLO_CUDA(params, rnn=rnn, mlp=mlp, **hp), ora
 
 
-def _run_both(family, case, steps, record, hp=None, nets=None):
+def _run_both(family, case, steps, record, hp=None, nets=None, after_step=None):
     """Drive the CUDA class and the oracle over the case's seeded inputs; {step: [tensors]} for both."""
     init = cases.init_values(case)
     params = [torch.nn.Parameter(v.cuda()) for v in init]
@@ -100,6 +110,8 @@ def _run_both(family, case, steps, record, hp=None, nets=None):
         else:
             opt.step()
             ora.step(ref, grads)
+        if after_step is not None:
+            after_step(t, opt, ora)
         if t in record:
             got[t] = [p.detach().cpu().clone() for p in params]
             want[t] = [r.clone() for r in ref]
@@ -120,11 +132,68 @@ def _assert_bounds(test, got, want, init, update_tol=UPDATE_TOL):
     assert all(u < update_tol for u in upd.values()), upd
 
 
-@pytest.mark.parametrize("family", FAMILIES)
-def test_bench_sample_matches_oracle(family):
+# (family, Newton-Schulz) pairs; the two families that have it run with and without
+SAMPLE_VARIANTS = [("adafaclo", None), ("elo", None), ("velo", None), ("celo2", False), ("elo_celo2", False),
+                   ("celo2", True), ("elo_celo2", True)]
+
+
+def _raw_steps(opt):
+    """The raw (pre Newton-Schulz) step of every learned-optimizer tensor of a CELO2-family optimizer, in plan order."""
+    out = []
+    for _, plan in opt._plans.values():
+        if plan["lo"] is not None:
+            out += [t.out.detach().cpu() for t in plan["lo"].tensors]
+    return out
+
+
+def _assert_newton_schulz_case(test, family, case, steps, hp):
+    """Large matrices with Newton-Schulz on: anchor on the fp64 oracle (see the module docstring)."""
+    from oracle import pylo_oracle as O
+
+    raw = {}
+
+    def keep_first_raw_step(t, opt, ora):
+        if t == 1:
+            raw["gpu"] = [r.clone() for r in _raw_steps(opt)]
+            raw["ref"] = [st["raw_step"].clone() for st in ora.state if "raw_step" in st]
+
+    got, want32, init, opt, ora32 = _run_both(family, case, steps, [steps], hp=hp, after_step=keep_first_raw_step)
+    # 1. what enters Newton-Schulz matches the oracle to the usual bound (first step: later ones start from
+    #    parameters that already carry the Newton-Schulz difference)
+    raw_gpu, raw_ref = raw["gpu"], raw["ref"]
+    assert len(raw_gpu) == len(raw_ref) > 0
+    worst_raw = 0.0
+    for a, b in zip(raw_gpu, raw_ref):
+        a, b = a.double().reshape(-1), b.double().reshape(-1)
+        worst_raw = max(worst_raw, float(((a - b).abs() / torch.maximum(b.abs(), b.pow(2).mean().sqrt())).max()))
+    # 2. the parameters: distance to the fp64 oracle, in units of the fp32 oracle's own distance to it
+    okw = dict(hp)
+    if family == "elo_celo2":
+        okw = dict(dict(clip_grad=True, adam_lr_mult=20.0), **okw)
+    ora64 = O.CELO2Oracle(_nets(family).flat_weights(), shared_adam=(family == "elo_celo2"), dtype=torch.float64, **okw)
+    ref64 = [v.double() for v in init]
+    for t in range(1, steps + 1):
+        ora64.step(ref64, [g.double() for g in cases.grads_at(case, t)])
+    want64 = {steps: [r.float() for r in ref64]}
+    e_gpu = CU.compare(got, want64, init)[steps]
+    e_cpu = CU.compare(want32, want64, init)[steps]
+    CU.log_parity(test, raw_step=worst_raw, gpu_vs_fp64_rel=e_gpu[0], gpu_vs_fp64_move=e_gpu[1], cpu32_vs_fp64_rel=e_cpu[0],
+                  cpu32_vs_fp64_move=e_cpu[1])
+    assert worst_raw < 1e-5, worst_raw
+    assert e_gpu[1] <= NS_FACTOR * e_cpu[1] + MOVE_TOL, (e_gpu, e_cpu)
+    assert e_gpu[0] <= NS_FACTOR * e_cpu[0] + REL_1STEP, (e_gpu, e_cpu)
+
+
+@pytest.mark.parametrize("family,newton_schulz", SAMPLE_VARIANTS)
+def test_bench_sample_matches_oracle(family, newton_schulz):
     """(1024, 4096) + (4096,): the matrix and the vector the benchmark's CPU leg is timed on."""
     case = dict(shapes=[(1024, 4096), (4096,)], init_seed=1, init_scale=0.02, grad_seed=2, **GRADS[family])
-    got, want, init, _, _ = _run_both(family, case, 3, [1, 3])
+    hp = dict(HP[family])
+    if newton_schulz is not None:
+        hp["orthogonalize"] = newton_schulz
+    if newton_schulz:
+        return _assert_newton_schulz_case(f"bench_sample[{family},ns]", family, case, 3, hp)
+    got, want, init, _, _ = _run_both(family, case, 3, [1, 3], hp=hp)
     _assert_bounds(f"bench_sample[{family}]", got, want, init)
 
 
@@ -135,8 +204,10 @@ def test_celo2_4096_config_matches_oracle(orthogonalize):
     case = dict(shapes=[(4096, 4096), (4096,)], init_seed=1, init_scale=0.02, grad_seed=2, grad_kind="rowlognormal",
                 log_mu=-7.0)
     hp = dict(lr=1e-3, weight_decay=0.1, orthogonalize=orthogonalize)
+    if orthogonalize:
+        return _assert_newton_schulz_case("celo2_4096[ns]", "celo2", case, 2, hp)
     got, want, init, _, _ = _run_both("celo2", case, 2, [1, 2], hp=hp)
-    _assert_bounds(f"celo2_4096[orth={int(orthogonalize)}]", got, want, init)
+    _assert_bounds("celo2_4096[ns off]", got, want, init)
 
 
 @pytest.mark.parametrize("family", FAMILIES)

@@ -2,8 +2,8 @@
 
 Tolerances, all fp32: 1e-5 relative per parameter element after one step and
 1e-4 after the full trajectory (up to 100 steps); in addition the *movement*
-of the parameters since initialisation must agree to 1e-4 of its largest
-entry, and the update of every single element to 1e-3 of max(|its update|, rms
+of the parameters since initialisation must agree to 2e-5 of its largest
+entry, and the update of every single element to 1e-4 of max(|its update|, rms
 update of its tensor): the sharper tests when the learning rate is small.
 """
 
@@ -18,8 +18,8 @@ pytestmark = pytest.mark.gpu
 
 REL_1STEP = 1e-5
 REL_END = 1e-4
-MOVE_TOL = 1e-4
-UPDATE_TOL = 1e-3
+MOVE_TOL = 2e-5     # observed: <= 2.3e-6
+UPDATE_TOL = 1e-4   # observed: <= 8.3e-6
 
 LO_CASES = sorted(G.CASES)
 

@@ -26,7 +26,7 @@ pytestmark = pytest.mark.gpu
 # cancel it); the (40,) and (257,) tensors take the one-dimensional branch
 SHAPES = [(96, 64), (64, 160), (300, 200), (40,), (257,)]
 FAMILIES = ["adafaclo", "elo", "celo2", "elo_celo2", "velo"]
-MOVE_TOL_VS_FAST_MATH = 5e-4
+MOVE_TOL_VS_FAST_MATH = 5e-5   # observed: <= 1.6e-6
 
 
 def _ref_cuda():

@@ -1,10 +1,9 @@
-"""GPU checks of the tensor-core variants of the AdafacLO / ELO apply kernel (``mlp_precision="3xtf32"`` and
-``"2xfp16"``).
+"""GPU checks of the tensor-core variant of the AdafacLO / ELO apply kernel (``mlp_precision="3xtf32"``, the default).
 
-The two hidden layers run as tcgen05 products with every operand split into a high and a low part (TF32, or
-fp16 with normalised features); the results must stay inside the same bounds as the scalar-FMA path: 1e-5 relative per element after one
-step, 1e-4 after the whole trajectory, movement within 1e-4 of its largest entry against the oracle, and
-within 1e-5 of the movement against the scalar-FMA path of the library itself at the full 4096 x 4096 size.
+The two hidden layers run as tcgen05 products with every operand split into a high and a low TF32 part; the
+results must stay inside the same bounds as the scalar-FMA path: 1e-5 relative per element after one step, 1e-4
+after the whole trajectory, movement within 2e-5 of its largest entry against the oracle, and within 1e-5 of the
+movement against the scalar-FMA path of the library itself at the full 4096 x 4096 size.
 """
 
 import pytest
@@ -16,8 +15,8 @@ import golden_util as G
 
 pytestmark = pytest.mark.gpu
 
-PRECISIONS = ["3xtf32", "2xfp16"]
-MOVE_TOL = 1e-4
+PRECISIONS = ["3xtf32"]
+MOVE_TOL = 2e-5
 ADAFAC_CASES = sorted(n for n, c in G.CASES.items() if c["family"] in ("adafaclo", "elo"))
 
 

@@ -1,15 +1,14 @@
-"""CPU emulation of the operand splits the tensor-core apply kernels use.
+"""CPU emulation of the operand split the tensor-core kernels use.
 
-The kernels feed the tensor cores operands of 11 significant bits (TF32, or fp16) and recover fp32 fidelity by
-splitting every operand into a high and a low part and accumulating three products per layer (lo x hi, hi x lo,
-hi x hi) in fp32.  This file restates the two splits with integer masks / torch casts and checks, against fp64,
-that a 32-term dot product comes out within a few 1e-7 of the sum of its terms' magnitudes - the same order as a
-plain fp32 FMA chain - and that a single 11-bit product does not (so the test can tell the difference).
+The kernels feed the tensor cores TF32 operands (11 significant bits) and recover fp32 fidelity by splitting every
+operand into a high and a low part and accumulating three products per layer (lo x hi, hi x lo, hi x hi) in fp32.
+This file restates the split with integer masks and checks, against fp64, that a 32-term dot product comes out
+within a few 1e-7 of the sum of its terms' magnitudes - the same order as a plain fp32 FMA chain - and that a
+single 11-bit product does not (so the test can tell the difference).
 """
 
 import numpy as np
 import pytest
-import torch
 
 
 def tf32_trunc(x: np.ndarray) -> np.ndarray:
@@ -23,12 +22,6 @@ def split_tf32(x):
     return hi, lo
 
 
-def split_fp16(x):
-    hi = torch.from_numpy(x).to(torch.float16)
-    lo = (torch.from_numpy(x) - hi.float()).to(torch.float16)
-    return hi.float().numpy(), lo.float().numpy()
-
-
 def three_products(a, b, split):
     """sum_k a[m,k] b[n,k] with fp32 accumulation of lo x hi, hi x lo, hi x hi (in that order)."""
     ah, al = split(a)
@@ -40,7 +33,7 @@ def three_products(a, b, split):
     return acc
 
 
-@pytest.mark.parametrize("name,split,scale", [("tf32", split_tf32, 1e-4), ("tf32", split_tf32, 1.0), ("fp16", split_fp16, 1.0)])
+@pytest.mark.parametrize("name,split,scale", [("tf32", split_tf32, 1e-4), ("tf32", split_tf32, 1.0)])
 def test_three_split_products_are_fp32_faithful(name, split, scale):
     rng = np.random.default_rng(0)
     a = (rng.standard_normal((128, 32)) * 3.0 * scale).astype(np.float32)
@@ -57,11 +50,3 @@ def test_three_split_products_are_fp32_faithful(name, split, scale):
     assert err < 8 * max(err_fp32, 6e-8), (name, err, err_fp32)
     single = np.max(np.abs(split(a)[0].astype(np.float64) @ split(b)[0].astype(np.float64).T - exact) / mag)
     assert single > 1e-5  # one 11-bit product alone is three orders worse: the split is what buys the accuracy
-
-
-def test_fp16_split_keeps_an_absolute_floor_for_small_values():
-    """Values far below 1 (the features are normalised to unit rms) lose relative, not absolute, precision."""
-    x = np.array([1e-3, 1e-5, 3e-7, 1.0, 250.0, 60000.0], dtype=np.float32)
-    hi, lo = split_fp16(x)
-    err = np.abs((hi.astype(np.float64) + lo.astype(np.float64)) - x.astype(np.float64))
-    assert np.all(err <= np.maximum(3.1e-8, np.abs(x) * 2.0 ** -21))
