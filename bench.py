@@ -62,8 +62,9 @@ def parse(argv=None):
     ap.add_argument("--optimizer", default="adafaclo", choices=sorted(STEP_BYTES))
     ap.add_argument("--layers", type=int, default=None, help="llama3_8b only: number of transformer layers (default 32)")
     ap.add_argument("--no-orthogonalize", action="store_true", help="celo2 family: skip Newton-Schulz")
-    ap.add_argument("--ns-precision", default="fp32", choices=["fp32", "3xtf32"],
-                    help="celo2 family: Newton-Schulz products in fp32 (reference arithmetic) or as three TF32 tensor-core GEMMs")
+    ap.add_argument("--ns-precision", default="3xtf32", choices=["fp32", "3xtf32"],
+                    help="celo2 family: Newton-Schulz products on the tensor cores by this library's kernel (operands split "
+                         "into TF32 high and low parts), or as fp32 torch.matmul (the reference's arithmetic; a library call)")
     ap.add_argument("--mlp-precision", default="3xtf32", choices=["fp32", "3xtf32"],
                     help="adafaclo / elo: the network's hidden layers as scalar fp32 FMAs, or as tensor-core products of "
                          "operands split into two TF32 parts (fp32-faithful: hi x hi + hi x lo + lo x hi)")
@@ -253,6 +254,8 @@ def config_of(args, shapes, n_gpus):
         "optimizer": args.optimizer, "shapes": args.workload, "tensors": len(shapes),
         "params": W.total_params(shapes), "grads": f"randn*{gscale} ({gkind}), one buffer per distinct shape",
         "orthogonalize": (not args.no_orthogonalize) if "celo2" in args.optimizer else None,
+        "newton_schulz": (None if "celo2" not in args.optimizer or args.no_orthogonalize else
+                          ("k_gemm_tn_3xtf32 (this library, tcgen05)" if args.ns_precision == "3xtf32" else "torch.matmul fp32 (library)")),
         "mlp_precision": args.mlp_precision if args.optimizer in ("adafaclo", "elo") else None,
         "cache": "inputs larger than L2 (no flush needed)" if W.total_params(shapes) * 24 / max(n_gpus, 1) > 2e9
                  else "L2 flushed between steps by writing a 512 MiB buffer",
@@ -543,10 +546,13 @@ def measure(args, dev, world, rank, local, headline):
 EXTRA_CONFIGS = [
     ("velo/gpt2_medium", "gpt2_medium", "velo", [], 50),
     ("celo2/celo2_4096/ns_off", "celo2_4096", "celo2", ["--no-orthogonalize"], 100),
-    ("celo2/celo2_4096/ns_on", "celo2_4096", "celo2", [], 20),
+    ("celo2/celo2_4096/ns_on", "celo2_4096", "celo2", [], 30),
+    ("celo2/celo2_4096/ns_on_torch_matmul", "celo2_4096", "celo2", ["--ns-precision=fp32"], 20),
     ("elo_celo2/vit_b16/ns_off", "vit_b16", "elo_celo2", ["--no-orthogonalize"], 100),
-    ("elo_celo2/vit_b16/ns_on", "vit_b16", "elo_celo2", [], 20),
+    ("elo_celo2/vit_b16/ns_on", "vit_b16", "elo_celo2", [], 30),
+    ("elo_celo2/vit_b16/ns_on_torch_matmul", "vit_b16", "elo_celo2", ["--ns-precision=fp32"], 20),
     ("celo2/llama3_8b/ns_off", "llama3_8b", "celo2", ["--no-orthogonalize"], 3),
+    ("celo2/llama3_8b/ns_on", "llama3_8b", "celo2", [], 1),
 ]
 
 
@@ -554,6 +560,7 @@ def compact(name, line):
     r = line["roofline"]
     return {"name": name, "workload": line["config"]["workload"], "ms_per_step": line["ms_per_step"], "steps": line["steps"],
             "value": line["value"], "unit": UNIT, "orthogonalize": line["config"]["orthogonalize"],
+            "newton_schulz": line["config"].get("newton_schulz"),
             "exchange": line["config"]["exchange"], "cache": line["config"]["cache"],
             "replica_check": line["config"].get("replica_check"),
             "roofline": {"step_frac": r["step"]["frac"], "step_bytes_per_param": r["step"]["algorithmic_bytes_per_param"],
@@ -584,6 +591,7 @@ def run_b200(args):
             sub = copy.copy(args)
             sub.workload, sub.optimizer, sub.steps, sub.warmup = workload, optimizer, steps, 3
             sub.no_orthogonalize = "--no-orthogonalize" in more
+            sub.ns_precision = "fp32" if "--ns-precision=fp32" in more else "3xtf32"
             if workload == "llama3_8b" and world == 1:
                 # 8.03 G parameters with the CELO2 family's 20 B/param of state do not fit one GPU: 16 of the 32 layers
                 sub.layers = 16

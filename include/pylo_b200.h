@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define PYLO_B200_ABI_VERSION 8
+#define PYLO_B200_ABI_VERSION 9
 
 /* optimizer families (which feature set / network geometry a launch uses) */
 #define PYLO_FAM_ADAFAC 0 /* AdafacLO_CUDA, ELO_CUDA: 28+11 features, 39-32-32-2 */
@@ -276,6 +276,28 @@ int pylo_b200_apply_adafac_tc(const pylo_tensor_desc* descs, const pylo_atile* t
  * for every family desc.h_b transposed, [H][Y]. */
 int pylo_b200_apply_packed(const pylo_tensor_desc* descs, const pylo_atile* ctiles, int n_ctiles,
                            const pylo_step_params* prm, void* stream);
+
+/* Batched fp32-faithful matrix product on the tensor cores, for the Newton-Schulz orthogonalisation of the CELO2
+ * family (orthogonalize_via_newton_schulz, CELO2_naive.py:59-73, called at CELO2_cuda.py:332-335; the reference runs
+ * it as torch.matmul):
+ *     C[b][m][n] = alpha * sum_k A[b][m][k] * B[b][n][k] + beta * D[b][m][n]        b < batch
+ * A is [M][K] with row pitch lda, B is [N][K] with row pitch ldb (both with K contiguous), C and D are [M][N].
+ * One round of the iteration is three calls: a = x x^T (A = B = x), b = c1 a + c2 a a (A = B = D = a, a being
+ * symmetric) and x' = c0 x + b x (A = b, B = x^T, D = x).  Every operand element is split into a TF32 high and low
+ * part inside the kernel and three tcgen05 products (lo x hi, hi x lo, hi x hi) are accumulated in fp32.
+ * Requirements (else -1): K, N and all pitches and batch strides multiples of 4, all pointers 16-byte aligned,
+ * D (may be NULL) different from C.  g is a HOST pointer.  status: device int, bit 2 is ORed in if a bounded wait
+ * inside the kernel ran out (the output is then incomplete); may be NULL. */
+typedef struct pylo_gemm_desc {
+  const float* A;
+  const float* B;
+  float* C;
+  const float* D;
+  int64_t strideA, strideB, strideC, strideD; /* distance in floats between consecutive matrices of the batch */
+  int32_t M, N, K, lda, ldb, ldc, ldd, batch;
+  float alpha, beta;
+} pylo_gemm_desc;
+int pylo_b200_gemm_tn_3xtf32(const pylo_gemm_desc* g, int* status, void* stream);
 
 /* CELO2 tail (CELO2_cuda.py:336-339): step * rsqrt(mean(step^2 over the last two axes) + 1e-9) * rmsmult,
  * then p -= lr * (step + wd * p).  Items are matrices (the last two axes of a tensor). */

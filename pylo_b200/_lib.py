@@ -16,7 +16,7 @@ SUMS_STRIDE = 48
 TILE_ELEMS = 16384
 A_COLS = 1024
 WFOLD_STRIDE = 2432
-ABI_VERSION = 8
+ABI_VERSION = 9
 
 FAM_ADAFAC, FAM_CELO2, FAM_VELO = 0, 1, 2
 MODE_FAST2D, MODE_GENERIC, MODE_VEC1D = 0, 1, 2
@@ -66,6 +66,14 @@ class WsLayout(C.Structure):
         (name, C.c_int32) for name in ("rb", "n_strips", "n_cb", "n_tiles")]
 
 
+class GemmDesc(C.Structure):
+    """pylo_gemm_desc: C[b] = alpha * A[b] @ B[b]^T + beta * D[b] with both operands K-major."""
+    _fields_ = [("A", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p), ("D", C.c_void_p),
+                ("strideA", C.c_int64), ("strideB", C.c_int64), ("strideC", C.c_int64), ("strideD", C.c_int64)] + [
+        (name, C.c_int32) for name in ("M", "N", "K", "lda", "ldb", "ldc", "ldd", "batch")] + [
+        ("alpha", C.c_float), ("beta", C.c_float)]
+
+
 class VeloRnn(C.Structure):
     _fields_ = [(name, C.c_void_p) for name in (
         "mix2_w", "mix2_b", "fmix_w", "fmix_b", "lstm_w", "lstm_b", "ctrl_w", "ctrl_b", "step_w", "step_b",
@@ -105,6 +113,7 @@ def _load():
         "pylo_b200_apply_adafac_cols": [vp, vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_apply_adafac_tc": [vp, vp, i32, C.POINTER(StepParams), vp, vp],
         "pylo_b200_apply_packed": [vp, vp, i32, C.POINTER(StepParams), vp],
+        "pylo_b200_gemm_tn_3xtf32": [C.POINTER(GemmDesc), vp, vp],
         "pylo_b200_celo2_post_sums": [vp, vp, i32, vp],
         "pylo_b200_celo2_post_apply": [vp, vp, i32, vp],
         "pylo_b200_adamw": [vp, vp, i32, i32, f32, f32, f32, f32, f32, C.POINTER(StepParams), vp],

@@ -9,7 +9,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_PATH = os.path.join(CSRC, "libpylo_b200.so")
 SOURCES = [os.path.join(CSRC, "pylo_kernels.cu")]
-HEADERS = [os.path.join(CSRC, "pylo_common.cuh"), os.path.join(CSRC, "pylo_apply_tc.cuh"), os.path.join(INCLUDE, "pylo_b200.h")]
+HEADERS = [os.path.join(CSRC, "pylo_common.cuh"), os.path.join(CSRC, "pylo_apply_tc.cuh"), os.path.join(CSRC, "pylo_ns_gemm.cuh"), os.path.join(INCLUDE, "pylo_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -8,6 +8,8 @@
 // All reductions go through fixed-slot partials and fixed-order final sums, so
 // results are bit-reproducible from run to run (no floating-point atomics).
 
+#include <string.h>
+
 #include <mutex>
 
 #include "pylo_common.cuh"
@@ -1048,6 +1050,7 @@ __global__ void __launch_bounds__(NT, CC_CTAS_PER_SM) k_apply_adafac_cols(const 
 }
 
 #include "pylo_apply_tc.cuh"
+#include "pylo_ns_gemm.cuh"
 
 // ================================================================================================
 // Phase C for CELO2 / ELO_CELO2 / VeLO on FAST2D tensors: packed kernel.
@@ -1810,6 +1813,27 @@ int pylo_b200_apply_adafac_tc(const pylo_tensor_desc* descs, const pylo_atile* t
   static bool configured[PYLO_MAX_DEVICES] = {};
   if (int rc = allow_dynamic_smem(k_apply_adafac_tc, smem, configured)) return rc;
   k_apply_adafac_tc<<<grid_for(n_ttiles, 1), TC_NT, smem, (cudaStream_t)stream>>>(descs, ttiles, n_ttiles, *prm, status);
+  return launch_status();
+}
+
+int pylo_b200_gemm_tn_3xtf32(const pylo_gemm_desc* g, int* status, void* stream) {
+  CHECK_ARG(g && g->A && g->B && g->C);
+  CHECK_ARG(g->M > 0 && g->N > 0 && g->K > 0 && g->batch > 0);
+  // rows are moved in 16-byte pieces
+  CHECK_ARG(g->K % 4 == 0 && g->N % 4 == 0 && g->lda % 4 == 0 && g->ldb % 4 == 0 && g->ldc % 4 == 0);
+  CHECK_ARG(g->lda >= g->K && g->ldb >= g->K && g->ldc >= g->N);
+  CHECK_ARG(((uintptr_t)g->A | (uintptr_t)g->B | (uintptr_t)g->C | (uintptr_t)g->D) % 16 == 0);
+  CHECK_ARG(g->strideA % 4 == 0 && g->strideB % 4 == 0 && g->strideC % 4 == 0);
+  if (g->D) CHECK_ARG(g->ldd % 4 == 0 && g->ldd >= g->N && g->strideD % 4 == 0 && g->D != g->C);
+  static_assert(sizeof(pylo_gemm_desc) == sizeof(pylo_gemm_args), "pylo_gemm_desc and the kernel's argument block differ");
+  pylo_gemm_args a;
+  memcpy(&a, g, sizeof(a));
+  const long long tiles = (long long)((g->M + NS_BM - 1) / NS_BM) * ((g->N + NS_BN - 1) / NS_BN) * g->batch;
+  static bool configured[PYLO_MAX_DEVICES] = {};
+  constexpr int smem = (int)sizeof(NsSmem) + 1024;  // room to start the tiles on a 1024-byte boundary
+  if (int rc = allow_dynamic_smem(k_gemm_tn_3xtf32, smem, configured)) return rc;
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  k_gemm_tn_3xtf32<<<grid, NS_THREADS, smem, (cudaStream_t)stream>>>(a, status);
   return launch_status();
 }
 

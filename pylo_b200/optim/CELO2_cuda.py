@@ -29,7 +29,8 @@ from torch.optim import Optimizer
 from .. import _lib as L
 from ..models.CELO2_MLP import CELO2MLP
 from ..plan import GradNorm, LoPlan, LoTensor, current_stream_ptr, one_minus
-from ._common import ItemPlan, factored_dims_argsort, newton_schulz, newton_schulz_3xtf32, require_cuda_param
+from ._common import (ItemPlan, factored_dims_argsort, newton_schulz, newton_schulz_eligible, newton_schulz_tc,
+                      require_cuda_param)
 
 _IN, _HID = 30, 8
 
@@ -72,7 +73,13 @@ class _Celo2Family(Optimizer):
         self._w_flat = torch.cat([t.reshape(-1) for t in (self.w_in, self.b_in, self.w_h, self.b_h, self.w_out, self.b_out)]).contiguous()
         self._plans = {}
         self._gnorm = None
-        self.ns_precision = "fp32"  # "3xtf32": Newton-Schulz products as three TF32 tensor-core GEMMs (not bit-identical)
+        # "3xtf32" (default): the Newton-Schulz products on the tensor cores (this library's kernel, operands split
+        # into TF32 high and low parts, as accurate as fp32 products); "fp32": torch.matmul, the reference's arithmetic
+        self.ns_precision = "3xtf32"
+        #: device word the Newton-Schulz kernel ORs 4 into if one of its bounded waits ran out
+        self._ns_status = torch.zeros(1, dtype=torch.int32, device=dev)
+        #: Newton-Schulz launches of this library since construction (for the benchmark's launch count)
+        self.extra_launches = 0
         self.process_group = None   # set (or set _sharded) when the tensors of the model are split over ranks
         self._sharded = False
         self.after_group = None     # optional callable(group index), called once a param group's kernels are enqueued
@@ -181,6 +188,11 @@ class _Celo2Family(Optimizer):
         prm.gnorm_sq = gnorm_ptr
         return prm
 
+    def check_status(self):
+        """Synchronise and raise if the Newton-Schulz kernel reported a wait that ran out (its output is incomplete)."""
+        if int(self._ns_status.item()) != 0:
+            raise L.PyloLibError(f"{self._name}: a wait inside the Newton-Schulz kernel timed out; the step is invalid")
+
     # ------------------------------------------------------------------ step
     @torch.no_grad()
     def step(self, loss=None):
@@ -227,12 +239,18 @@ class _Celo2Family(Optimizer):
                 post = plan["post"]
                 keep = [t.out for t in lo.tensors]
                 if group["orthogonalize"]:
-                    ns = newton_schulz_3xtf32 if self.ns_precision == "3xtf32" else newton_schulz
                     for stacked, members in plan["stacks"]:
+                        on_tc = self.ns_precision == "3xtf32" and newton_schulz_eligible(*stacked.shape[-2:])
                         # batches of at most ~64 M elements keep the iteration's temporaries small
                         per = max(1, (64 << 20) // max(1, stacked[0].numel()))
                         for c0 in range(0, len(members), per):
-                            res = ns(stacked[c0:c0 + per], self.ns_coeffs, self.ns_iters, self.ns_eps).contiguous()
+                            part = stacked[c0:c0 + per]
+                            if on_tc:
+                                res = newton_schulz_tc(part, self.ns_coeffs, self.ns_iters, self.ns_eps, self._ns_status, stream)
+                                self.extra_launches += 3 * self.ns_iters
+                            else:
+                                res = newton_schulz(part, self.ns_coeffs, self.ns_iters, self.ns_eps)
+                            res = res.contiguous()
                             for j, ti in enumerate(members[c0:c0 + per]):
                                 keep[ti] = res[j]
                 it = post.items
@@ -294,7 +312,7 @@ class CELO2_CUDA(_Celo2Family):
                  initial_rms_decays=(0.95,), initial_adafactor_decays=(0.9, 0.99, 0.999), exp_mult=0.0, rmsmult=1.0,
                  param_scale_mult=False, ns_coeffs=(3.4445, -4.7750, 2.0315), ns_iters=5, ns_eps=1e-8,
                  grad_clip_val=1000.0, hf_key: Optional[str] = "DiamondXL/celo2",
-                 checkpoint_path: Optional[str] = None, network: Optional[CELO2MLP] = None, ns_precision: str = "fp32"):
+                 checkpoint_path: Optional[str] = None, network: Optional[CELO2MLP] = None, ns_precision: str = "3xtf32"):
         defaults = dict(
             lr=lr, weight_decay=weight_decay, adam_lr_mult=adam_lr_mult,
             adam_weight_decay=(adam_weight_decay if adam_weight_decay is not None else weight_decay),
@@ -322,7 +340,7 @@ class ELO_CELO2_CUDA(_Celo2Family):
                  initial_adafactor_decays=(0.9, 0.99, 0.999), exp_mult=0.0, rmsmult=1.0, param_scale_mult=False,
                  ns_coeffs=(3.4445, -4.7750, 2.0315), ns_iters=5, ns_eps=1e-8, grad_clip_val=1000.0,
                  hf_key: Optional[str] = "DiamondXL/elo-celo2", checkpoint_path: Optional[str] = None,
-                 network: Optional[CELO2MLP] = None, ns_precision: str = "fp32"):
+                 network: Optional[CELO2MLP] = None, ns_precision: str = "3xtf32"):
         defaults = dict(
             lr=lr, weight_decay=weight_decay, adam_lr_mult=adam_lr_mult,
             adam_weight_decay=(adam_weight_decay if adam_weight_decay is not None else weight_decay),

@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-import ctypes as C
+import ctypes as C_
 from typing import List, Optional, Sequence
 
 import numpy as np
@@ -60,50 +60,62 @@ def newton_schulz(x: torch.Tensor, coeffs, iters: int = 5, eps: float = 1e-8) ->
     return x.transpose(-2, -1) if tall else x
 
 
-def _split_tf32(x: torch.Tensor):
-    """x = hi + lo (+ a remainder below 2^-22 |x|): hi is x rounded to nearest TF32 (10 mantissa bits), lo
-    the exact difference rounded to TF32 as well, so that the tensor core's own truncation of its inputs
-    loses nothing."""
-    def to_tf32(t):
-        return ((t.view(torch.int32) + 0x1000) & -8192).view(torch.float32)
+def _gemm_tn(A, B, C, D, alpha, beta, status, stream):
+    """C[b] = alpha * A[b] @ B[b]^T + beta * D[b] through ``pylo_b200_gemm_tn_3xtf32`` (3-D contiguous fp32 tensors)."""
+    g = L.GemmDesc()
+    g.A, g.B, g.C, g.D = A.data_ptr(), B.data_ptr(), C.data_ptr(), (D.data_ptr() if D is not None else None)
+    g.batch, g.M, g.K = A.shape
+    g.N = B.shape[1]
+    g.lda, g.ldb, g.ldc, g.ldd = A.stride(1), B.stride(1), C.stride(1), (D.stride(1) if D is not None else 0)
+    g.strideA, g.strideB, g.strideC = A.stride(0), B.stride(0), C.stride(0)
+    g.strideD = D.stride(0) if D is not None else 0
+    g.alpha, g.beta = float(alpha), float(beta)
+    L.check(L.lib.pylo_b200_gemm_tn_3xtf32(C_.byref(g), status.data_ptr() if status is not None else None, stream),
+            "gemm_tn_3xtf32")
 
-    hi = to_tf32(x)
-    return hi, to_tf32(x - hi)
+
+def newton_schulz_eligible(rows: int, cols: int) -> bool:
+    """Whether :func:`newton_schulz_tc` takes a matrix of this shape (else it goes to ``torch.matmul``): both sides
+    multiples of 4 (rows are moved in 16-byte pieces) and the short side at least 64 (the kernel's tiles have 128
+    rows; below half a tile the library product is the better tool)."""
+    r, c = min(rows, cols), max(rows, cols)
+    return r % 4 == 0 and c % 4 == 0 and r >= 64
 
 
-def _mm_3xtf32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """a @ b from three TF32 tensor-core products, a_hi b_hi + (a_hi b_lo + a_lo b_hi).
+def newton_schulz_tc(x: torch.Tensor, coeffs, iters: int = 5, eps: float = 1e-8, status=None, stream=None) -> torch.Tensor:
+    """:func:`newton_schulz` with the three products of every round on the tensor cores.
 
-    The dropped term a_lo b_lo is ~2^-22 of the result, so the product carries fp32-like accuracy while
-    running on the tensor cores; the GEMMs themselves are the library's (cuBLAS through torch.matmul).
+    Same chain as CELO2_naive.py:59-73.  Each product is one launch of the library's own batched kernel
+    (``pylo_b200_gemm_tn_3xtf32``: operands split into TF32 high and low parts inside the kernel, three tcgen05
+    products accumulated in fp32, the scaled additions ``c1 a + c2 (a a)`` and ``c0 x + (b x)`` as its epilogue),
+    which needs both operands with the contraction index contiguous; x^T is therefore kept beside x and refreshed
+    once per round.  Not bit-identical to the fp32 products of ``torch.matmul`` (neither are two builds of cuBLAS);
+    against an fp64 evaluation it is as close as they are.
     """
-    ah, al = _split_tf32(a)
-    bh, bl = _split_tf32(b)
-    return ah @ bh + (ah @ bl + al @ bh)
-
-
-def newton_schulz_3xtf32(x: torch.Tensor, coeffs, iters: int = 5, eps: float = 1e-8) -> torch.Tensor:
-    """:func:`newton_schulz` with every matrix product evaluated by :func:`_mm_3xtf32`.
-
-    Optional (``ns_precision="3xtf32"``) and off by default: it is not the reference's arithmetic.  Measured
-    against an fp64 evaluation its result is ~3e-5 off in relative Frobenius norm where the fp32 products
-    are ~4e-6 off (the TF32 units accumulate less exactly); on a 4096 x 4096 matrix it is 2.7x faster.
-    """
-    prev = torch.backends.cuda.matmul.allow_tf32
-    torch.backends.cuda.matmul.allow_tf32 = True
-    try:
-        tall = x.shape[-2] > x.shape[-1]
-        if tall:
-            x = x.transpose(-2, -1)
-        x = x / (torch.linalg.norm(x, dim=(-2, -1), keepdim=True) + eps)
-        c0, c1, c2 = coeffs
-        for _ in range(iters):
-            a = _mm_3xtf32(x, x.transpose(-2, -1).contiguous())
-            b = c1 * a + c2 * _mm_3xtf32(a, a)
-            x = c0 * x + _mm_3xtf32(b, x)
-        return x.transpose(-2, -1) if tall else x
-    finally:
-        torch.backends.cuda.matmul.allow_tf32 = prev
+    shape = x.shape
+    x = x.reshape((-1,) + tuple(shape[-2:]))
+    tall = x.shape[-2] > x.shape[-1]
+    if tall:
+        x = x.transpose(-2, -1)
+    x = (x / (torch.linalg.norm(x, dim=(-2, -1), keepdim=True) + eps)).contiguous()
+    n_b, r, c = x.shape
+    if stream is None:
+        stream = torch.cuda.current_stream().cuda_stream
+    c0, c1, c2 = (float(v) for v in coeffs)
+    xt = x.transpose(-2, -1).contiguous()
+    a = torch.empty((n_b, r, r), dtype=torch.float32, device=x.device)
+    b = torch.empty_like(a)
+    x_next = torch.empty_like(x)
+    for it in range(iters):
+        _gemm_tn(x, x, a, None, 1.0, 0.0, status, stream)          # a = x x^T
+        _gemm_tn(a, a, b, a, c2, c1, status, stream)               # b = c1 a + c2 a a   (a is symmetric)
+        _gemm_tn(b, xt, x_next, x, 1.0, c0, status, stream)        # x = c0 x + b x
+        x, x_next = x_next, x
+        if it + 1 < iters:
+            xt = x.transpose(-2, -1).contiguous()
+    if tall:
+        x = x.transpose(-2, -1)
+    return x.reshape(shape)
 
 
 def require_cuda_param(p: torch.Tensor, who: str):

@@ -84,7 +84,7 @@ def _make_pair(family, shapes, params, hp=None, nets=None):
         return cls(params, network=net, **hp), O.AdafacLOOracle(net.flat_weights(), elo=(family == "elo"), **hp)
     if family in ("celo2", "elo_celo2"):
         cls = optim.CELO2_CUDA if family == "celo2" else optim.ELO_CELO2_CUDA
-        okw = dict(hp)
+        okw = {k: v for k, v in hp.items() if k != "ns_precision"}  # where the products run is not the oracle's business
         if family == "elo_celo2":
             okw = dict(dict(clip_grad=True, adam_lr_mult=20.0), **okw)  # the CUDA class's own defaults
         return cls(params, network=net, **hp), O.CELO2Oracle(net.flat_weights(), shared_adam=(family == "elo_celo2"), **okw)
@@ -134,7 +134,7 @@ def _assert_bounds(test, got, want, init, update_tol=UPDATE_TOL):
 
 # (family, Newton-Schulz) pairs; the two families that have it run with and without
 SAMPLE_VARIANTS = [("adafaclo", None), ("elo", None), ("velo", None), ("celo2", False), ("elo_celo2", False),
-                   ("celo2", True), ("elo_celo2", True)]
+                   ("celo2", "fp32"), ("elo_celo2", "fp32"), ("celo2", "3xtf32"), ("elo_celo2", "3xtf32")]
 
 
 def _raw_steps(opt):
@@ -167,7 +167,7 @@ def _assert_newton_schulz_case(test, family, case, steps, hp):
         a, b = a.double().reshape(-1), b.double().reshape(-1)
         worst_raw = max(worst_raw, float(((a - b).abs() / torch.maximum(b.abs(), b.pow(2).mean().sqrt())).max()))
     # 2. the parameters: distance to the fp64 oracle, in units of the fp32 oracle's own distance to it
-    okw = dict(hp)
+    okw = {k: v for k, v in hp.items() if k != "ns_precision"}
     if family == "elo_celo2":
         okw = dict(dict(clip_grad=True, adam_lr_mult=20.0), **okw)
     ora64 = O.CELO2Oracle(_nets(family).flat_weights(), shared_adam=(family == "elo_celo2"), dtype=torch.float64, **okw)
@@ -190,22 +190,24 @@ def test_bench_sample_matches_oracle(family, newton_schulz):
     case = dict(shapes=[(1024, 4096), (4096,)], init_seed=1, init_scale=0.02, grad_seed=2, **GRADS[family])
     hp = dict(HP[family])
     if newton_schulz is not None:
-        hp["orthogonalize"] = newton_schulz
-    if newton_schulz:
-        return _assert_newton_schulz_case(f"bench_sample[{family},ns]", family, case, 3, hp)
+        hp["orthogonalize"] = bool(newton_schulz)
+    if newton_schulz:   # "fp32": torch.matmul, "3xtf32": the library's tensor-core kernel
+        hp["ns_precision"] = newton_schulz
+        return _assert_newton_schulz_case(f"bench_sample[{family},ns {newton_schulz}]", family, case, 3, hp)
     got, want, init, _, _ = _run_both(family, case, 3, [1, 3], hp=hp)
     _assert_bounds(f"bench_sample[{family}]", got, want, init)
 
 
-@pytest.mark.parametrize("orthogonalize", [False, True])
+@pytest.mark.parametrize("orthogonalize", [False, "fp32", "3xtf32"])
 def test_celo2_4096_config_matches_oracle(orthogonalize):
     """CELO2 on one 4096 x 4096 weight + a 4096 bias, per-row log-normal gradients (mu = -7, sigma = 1),
     weight decay 0.1, Newton-Schulz on and off (its fifteen 4096^3 products run on the CPU in the oracle)."""
     case = dict(shapes=[(4096, 4096), (4096,)], init_seed=1, init_scale=0.02, grad_seed=2, grad_kind="rowlognormal",
                 log_mu=-7.0)
-    hp = dict(lr=1e-3, weight_decay=0.1, orthogonalize=orthogonalize)
+    hp = dict(lr=1e-3, weight_decay=0.1, orthogonalize=bool(orthogonalize))
     if orthogonalize:
-        return _assert_newton_schulz_case("celo2_4096[ns]", "celo2", case, 2, hp)
+        hp["ns_precision"] = orthogonalize
+        return _assert_newton_schulz_case(f"celo2_4096[ns {orthogonalize}]", "celo2", case, 2, hp)
     got, want, init, _, _ = _run_both("celo2", case, 2, [1, 2], hp=hp)
     _assert_bounds("celo2_4096[ns off]", got, want, init)
 

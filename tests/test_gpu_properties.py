@@ -204,30 +204,12 @@ def test_full_size_is_bit_reproducible():
     assert torch.equal(outs[0], outs[1])
 
 
-def test_newton_schulz_3xtf32_error_is_bounded():
-    """Against an fp64 evaluation the fp32 Newton-Schulz is ~4e-6 off (the iteration amplifies rounding
-    noise: its polynomial has slope ~3.4 at zero); the optional tensor-core variant, whose products are
-    accumulated by the TF32 units, is ~3e-5 off.  Both stay far inside what the parameter update can see
-    once the result is normalised and multiplied by the learning rate."""
-    from pylo_b200.optim._common import newton_schulz, newton_schulz_3xtf32
-
-    gen = torch.Generator(device="cuda").manual_seed(5)
-    coeffs = (3.4445, -4.7750, 2.0315)
-    before = torch.backends.cuda.matmul.allow_tf32
-    for shape in [(768, 2304), (1024, 1024), (300, 200), (3, 64, 48)]:
-        x = torch.randn(shape, device="cuda", generator=gen)
-        exact = newton_schulz(x.double(), coeffs)
-        e32 = float((newton_schulz(x, coeffs).double() - exact).norm() / exact.norm())
-        e3x = float((newton_schulz_3xtf32(x, coeffs).double() - exact).norm() / exact.norm())
-        assert e32 < 2e-5 and e3x < 1e-4, (shape, e32, e3x)
-    assert torch.backends.cuda.matmul.allow_tf32 == before  # the global switch is restored
-
-
 def test_celo2_with_3xtf32_newton_schulz_stays_within_the_reference_bound():
     meta, weights, golden, _ = G.load("celo2_ref_orth1_exp0.0")
     case = dict(G.CASES["celo2_ref_orth1_exp0.0"])
     case["hparams"] = dict(case["hparams"], ns_precision="3xtf32")
-    got, _, _ = CU.run_cuda(case, weights)
+    got, opt, _ = CU.run_cuda(case, weights)
+    opt.check_status()
     assert G.max_abs_diff(got, golden) < 1e-5   # the bound of tests/test_celo2_cuda.py:95
 
 
