@@ -25,6 +25,7 @@ it does not load the CUDA library of this package.
 
 import argparse
 import copy
+import gc
 import json
 import os
 import subprocess
@@ -308,7 +309,10 @@ def measure(args, dev, world, rank, local, headline):
     total = W.total_params(shapes)
     gscale, gkind = grad_spec(args)
 
-    # memory guard: never drive the box out of memory
+    # memory guard: never drive the box out of memory (the previous configuration's optimizer sits in reference
+    # cycles through its hooks until the collector has run)
+    gc.collect()
+    torch.cuda.empty_cache()
     free, _ = torch.cuda.mem_get_info()
     state_bytes = 16 if args.optimizer not in ("celo2", "elo_celo2") else 20
     need = total * 4 + (total / world) * (state_bytes + 1) * 1.02 + 4e9

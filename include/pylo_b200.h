@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define PYLO_B200_ABI_VERSION 9
+#define PYLO_B200_ABI_VERSION 10
 
 /* optimizer families (which feature set / network geometry a launch uses) */
 #define PYLO_FAM_ADAFAC 0 /* AdafacLO_CUDA, ELO_CUDA: 28+11 features, 39-32-32-2 */
@@ -296,8 +296,17 @@ typedef struct pylo_gemm_desc {
   int64_t strideA, strideB, strideC, strideD; /* distance in floats between consecutive matrices of the batch */
   int32_t M, N, K, lda, ldb, ldc, ldd, batch;
   float alpha, beta;
+  int32_t symmetric; /* != 0: M == N and the result is symmetric (x x^T, a a): only the tiles that touch the diagonal or
+                        lie above it are computed; complete C with pylo_b200_transpose(mirror = 1) afterwards */
+  int32_t pad_;
 } pylo_gemm_desc;
 int pylo_b200_gemm_tn_3xtf32(const pylo_gemm_desc* g, int* status, void* stream);
+
+/* Batched transposes for the Newton-Schulz chain.  mirror == 0: dst[b][j][i] = src[b][i][j] for [rows][cols]
+ * matrices (src != dst).  mirror != 0: in place on square matrices (src == dst): everything below the diagonal
+ * becomes the mirror image of what is above it. */
+int pylo_b200_transpose(const float* src, float* dst, int rows, int cols, int ld_src, int ld_dst, int64_t stride_src,
+                        int64_t stride_dst, int batch, int mirror, void* stream);
 
 /* CELO2 tail (CELO2_cuda.py:336-339): step * rsqrt(mean(step^2 over the last two axes) + 1e-9) * rmsmult,
  * then p -= lr * (step + wd * p).  Items are matrices (the last two axes of a tensor). */

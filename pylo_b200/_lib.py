@@ -16,7 +16,7 @@ SUMS_STRIDE = 48
 TILE_ELEMS = 16384
 A_COLS = 1024
 WFOLD_STRIDE = 2432
-ABI_VERSION = 9
+ABI_VERSION = 10
 
 FAM_ADAFAC, FAM_CELO2, FAM_VELO = 0, 1, 2
 MODE_FAST2D, MODE_GENERIC, MODE_VEC1D = 0, 1, 2
@@ -71,7 +71,7 @@ class GemmDesc(C.Structure):
     _fields_ = [("A", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p), ("D", C.c_void_p),
                 ("strideA", C.c_int64), ("strideB", C.c_int64), ("strideC", C.c_int64), ("strideD", C.c_int64)] + [
         (name, C.c_int32) for name in ("M", "N", "K", "lda", "ldb", "ldc", "ldd", "batch")] + [
-        ("alpha", C.c_float), ("beta", C.c_float)]
+        ("alpha", C.c_float), ("beta", C.c_float), ("symmetric", C.c_int32), ("pad_", C.c_int32)]
 
 
 class VeloRnn(C.Structure):
@@ -114,6 +114,7 @@ def _load():
         "pylo_b200_apply_adafac_tc": [vp, vp, i32, C.POINTER(StepParams), vp, vp],
         "pylo_b200_apply_packed": [vp, vp, i32, C.POINTER(StepParams), vp],
         "pylo_b200_gemm_tn_3xtf32": [C.POINTER(GemmDesc), vp, vp],
+        "pylo_b200_transpose": [vp, vp, i32, i32, i32, i32, C.c_int64, C.c_int64, i32, i32, vp],
         "pylo_b200_celo2_post_sums": [vp, vp, i32, vp],
         "pylo_b200_celo2_post_apply": [vp, vp, i32, vp],
         "pylo_b200_adamw": [vp, vp, i32, i32, f32, f32, f32, f32, f32, C.POINTER(StepParams), vp],

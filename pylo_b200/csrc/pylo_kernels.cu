@@ -1828,12 +1828,24 @@ int pylo_b200_gemm_tn_3xtf32(const pylo_gemm_desc* g, int* status, void* stream)
   static_assert(sizeof(pylo_gemm_desc) == sizeof(pylo_gemm_args), "pylo_gemm_desc and the kernel's argument block differ");
   pylo_gemm_args a;
   memcpy(&a, g, sizeof(a));
-  const long long tiles = (long long)((g->M + NS_BM - 1) / NS_BM) * ((g->N + NS_BN - 1) / NS_BN) * g->batch;
+  if (g->symmetric) CHECK_ARG(g->M == g->N);
+  const long long tiles = (long long)ns_tiles_per_matrix((g->M + NS_BM - 1) / NS_BM, (g->N + NS_BN - 1) / NS_BN, g->symmetric) * g->batch;
   static bool configured[PYLO_MAX_DEVICES] = {};
   constexpr int smem = (int)sizeof(NsSmem) + 1024;  // room to start the tiles on a 1024-byte boundary
   if (int rc = allow_dynamic_smem(k_gemm_tn_3xtf32, smem, configured)) return rc;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   k_gemm_tn_3xtf32<<<grid, NS_THREADS, smem, (cudaStream_t)stream>>>(a, status);
+  return launch_status();
+}
+
+int pylo_b200_transpose(const float* src, float* dst, int rows, int cols, int ld_src, int ld_dst, int64_t stride_src,
+                        int64_t stride_dst, int batch, int mirror, void* stream) {
+  CHECK_ARG(src && dst && rows > 0 && cols > 0 && batch > 0 && batch <= 65535 && ld_src >= cols);
+  if (mirror) CHECK_ARG(rows == cols && src == dst && ld_src == ld_dst);
+  else CHECK_ARG(src != dst && ld_dst >= rows);
+  const dim3 grid((cols + 31) / 32, (rows + 31) / 32, batch);
+  CHECK_ARG(grid.y <= 65535);
+  k_transpose32<<<grid, 256, 0, (cudaStream_t)stream>>>(src, dst, rows, cols, ld_src, ld_dst, stride_src, stride_dst, mirror ? 1 : 0);
   return launch_status();
 }
 

@@ -6,8 +6,11 @@
 // The three products of one Newton-Schulz round (CELO2_naive.py:59-73: a = x x^T, b = c1 a + c2 a a, x = c0 x + b x)
 // all have this form once x^T is kept beside x (a is symmetric, so a a = a a^T), with the scaled additions as the
 // epilogue.  The operands are plain fp32 matrices; fp32 accuracy comes from splitting every operand element into a
-// TF32 high part and a TF32 low part (x & 0xffffe000, x - hi, both exact) and accumulating lo x hi, hi x lo and
+// TF32 high part (x rounded to nearest) and a low part (the exact remainder) and accumulating lo x hi, hi x lo and
 // hi x hi in the fp32 accumulator, small terms first.
+//
+// symmetric != 0 (M = N, the result is known to be symmetric, as x x^T and a a are): only the tiles that reach the
+// diagonal or lie above it are computed; the part below the diagonal is left untouched for k_mirror_lower.
 //
 // The tensor core adds into its fp32 accumulator with truncation, so a long accumulation drifts (measured: 3e-6 of
 // sum |a||b| after K = 3072 against 3e-7 for an fp32 FMA chain).  The contraction is therefore cut into chunks of
@@ -69,12 +72,38 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
         "r"(r[30]), "r"(r[31]) : "memory");
 }
 
+// x rounded to the nearest TF32 value (10 explicit mantissa bits), as an fp32 number
+__device__ __forceinline__ float tf32_rn(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
 struct pylo_gemm_args {  // mirrors pylo_gemm_desc (passed by value)
   const float* A; const float* B; float* C; const float* D;
   long long sA, sB, sC, sD;   // batch strides in floats
   int M, N, K, lda, ldb, ldc, ldd, batch;
   float alpha, beta;
+  int symmetric, pad_;
 };
+
+// Tiles of one matrix in the order they are taken: all of them, or (symmetric) for every row of tiles only those
+// whose 256 columns are not entirely below the diagonal of its 128 rows, i.e. tn >= tm / 2.
+__host__ __device__ inline int ns_tiles_per_matrix(int tiles_m, int tiles_n, int symmetric) {
+  if (!symmetric) return tiles_m * tiles_n;
+  int n = 0;
+  for (int tm = 0; tm < tiles_m; ++tm) n += tiles_n > tm / 2 ? tiles_n - tm / 2 : 0;
+  return n;
+}
+__device__ __forceinline__ void ns_tile_coords(int r, int tiles_m, int tiles_n, int symmetric, int& tm, int& tn) {
+  if (!symmetric) { tm = r / tiles_n; tn = r % tiles_n; return; }
+  for (tm = 0; tm < tiles_m; ++tm) {
+    const int cnt = tiles_n > tm / 2 ? tiles_n - tm / 2 : 0;
+    if (r < cnt) { tn = tm / 2 + r; return; }
+    r -= cnt;
+  }
+  tm = 0; tn = 0;
+}
 
 __device__ __forceinline__ bool ns_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
   const uint32_t a = smem_addr(bar);
@@ -125,7 +154,7 @@ __global__ void __launch_bounds__(NS_THREADS, 1) k_gemm_tn_3xtf32(const pylo_gem
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;   // columns [0,256): chunk accumulator, [256,512): running sum
   const int tiles_m = (g.M + NS_BM - 1) / NS_BM, tiles_n = (g.N + NS_BN - 1) / NS_BN;
-  const int tiles_per_batch = tiles_m * tiles_n;
+  const int tiles_per_batch = ns_tiles_per_matrix(tiles_m, tiles_n, g.symmetric);
   const long long n_tiles = (long long)tiles_per_batch * g.batch;
   const int n_kb = (g.K + NS_BK - 1) / NS_BK;
   const int n_chunks = (n_kb + NS_KCHUNK_BLOCKS - 1) / NS_KCHUNK_BLOCKS;
@@ -137,7 +166,8 @@ __global__ void __launch_bounds__(NS_THREADS, 1) k_gemm_tn_3xtf32(const pylo_gem
     bool dead = false;
     for (long long tile = blockIdx.x; tile < n_tiles && !dead && !sm.abort; tile += gridDim.x) {
       const int b = (int)(tile / tiles_per_batch), r = (int)(tile % tiles_per_batch);
-      const int tm = r / tiles_n, tn = r % tiles_n;
+      int tm, tn;
+      ns_tile_coords(r, tiles_m, tiles_n, g.symmetric, tm, tn);
       const int m = tm * NS_BM + warp * 32 + lane;
       const bool row_ok = m < g.M;
       float* crow = g.C + (long long)b * g.sC + (long long)(row_ok ? m : 0) * g.ldc;
@@ -226,7 +256,8 @@ __global__ void __launch_bounds__(NS_THREADS, 1) k_gemm_tn_3xtf32(const pylo_gem
     bool dead = false;
     for (long long tile = blockIdx.x; tile < n_tiles && !dead && !sm.abort; tile += gridDim.x) {
       const int b = (int)(tile / tiles_per_batch), r = (int)(tile % tiles_per_batch);
-      const int tm = r / tiles_n, tn = r % tiles_n;
+      int tm, tn;
+      ns_tile_coords(r, tiles_m, tiles_n, g.symmetric, tm, tn);
       const float* Ab = g.A + (long long)b * g.sA;
       const float* Bb = g.B + (long long)b * g.sB;
       for (int kb = 0; kb < n_kb; ++kb, ++kb_count) {
@@ -251,8 +282,11 @@ __global__ void __launch_bounds__(NS_THREADS, 1) k_gemm_tn_3xtf32(const pylo_gem
           const bool isA = u < 32;
           const int row = (isA ? u : u - 32) * 4 + r4;
           const int off = ns_swz(row, c8) / 4;
+          // high part = x rounded to the nearest TF32 value, low part = the exact remainder (the tensor core drops
+          // its last bits): what is lost is at most 2^-23 of |x| and has no preferred sign; masking the low bits of x
+          // off instead would lose up to 2^-22 and always downwards
           const float4 x = v[i];
-          const float4 hi = make_float4(tf32_hi(x.x), tf32_hi(x.y), tf32_hi(x.z), tf32_hi(x.w));
+          const float4 hi = make_float4(tf32_rn(x.x), tf32_rn(x.y), tf32_rn(x.z), tf32_rn(x.w));
           const float4 lo = make_float4(x.x - hi.x, x.y - hi.y, x.z - hi.z, x.w - hi.w);
           st4((isA ? st.a_hi : st.b_hi) + off, hi);
           st4((isA ? st.a_lo : st.b_lo) + off, lo);
@@ -267,4 +301,29 @@ __global__ void __launch_bounds__(NS_THREADS, 1) k_gemm_tn_3xtf32(const pylo_gem
   __syncthreads();
   if (tid == 0 && sm.abort && status) atomicOr(status, 4);
   if (warp == NS_EPI_WARPS) tc_dealloc(tmem, 512);
+}
+
+// Batched 32 x 32-tile transposes through shared memory.
+//   mode 0: dst[b][j][i] = src[b][i][j] for an [R][C] matrix (the x^T that the third product of a round reads);
+//   mode 1: in place on a square [R][R] matrix: the part below the diagonal becomes the mirror image of the part above
+//           it (completes the symmetric products; the diagonal tiles are mirrored inside the tile).
+__global__ void __launch_bounds__(256) k_transpose32(const float* __restrict__ src, float* __restrict__ dst, int R, int C,
+                                                     int lds, int ldd, long long ss, long long sd, int mode) {
+  __shared__ float tile[32][33];
+  const int b = blockIdx.z, ti = blockIdx.y, tj = blockIdx.x;
+  if (mode == 1 && tj < ti) return;  // source tiles: on and above the diagonal
+  const float* s = src + (long long)b * ss;
+  float* d = dst + (long long)b * sd;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int i = ti * 32 + ty + 8 * q, j = tj * 32 + tx;
+    if (i < R && j < C) tile[ty + 8 * q][tx] = s[(long long)i * lds + j];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int j = tj * 32 + ty + 8 * q, i = ti * 32 + tx;   // destination element (j, i)
+    if (i < R && j < C && (mode == 0 || j > i)) d[(long long)j * ldd + i] = tile[tx][ty + 8 * q];
+  }
 }

@@ -60,8 +60,10 @@ def newton_schulz(x: torch.Tensor, coeffs, iters: int = 5, eps: float = 1e-8) ->
     return x.transpose(-2, -1) if tall else x
 
 
-def _gemm_tn(A, B, C, D, alpha, beta, status, stream):
-    """C[b] = alpha * A[b] @ B[b]^T + beta * D[b] through ``pylo_b200_gemm_tn_3xtf32`` (3-D contiguous fp32 tensors)."""
+def _gemm_tn(A, B, C, D, alpha, beta, status, stream, symmetric=False):
+    """C[b] = alpha * A[b] @ B[b]^T + beta * D[b] through ``pylo_b200_gemm_tn_3xtf32`` (3-D fp32 tensors whose last axis is
+    contiguous).  ``symmetric``: the result is known to be symmetric; only the tiles on and above the diagonal are
+    computed and the rest is filled in by mirroring."""
     g = L.GemmDesc()
     g.A, g.B, g.C, g.D = A.data_ptr(), B.data_ptr(), C.data_ptr(), (D.data_ptr() if D is not None else None)
     g.batch, g.M, g.K = A.shape
@@ -70,8 +72,19 @@ def _gemm_tn(A, B, C, D, alpha, beta, status, stream):
     g.strideA, g.strideB, g.strideC = A.stride(0), B.stride(0), C.stride(0)
     g.strideD = D.stride(0) if D is not None else 0
     g.alpha, g.beta = float(alpha), float(beta)
+    g.symmetric = int(bool(symmetric))
     L.check(L.lib.pylo_b200_gemm_tn_3xtf32(C_.byref(g), status.data_ptr() if status is not None else None, stream),
             "gemm_tn_3xtf32")
+    if symmetric:
+        L.check(L.lib.pylo_b200_transpose(C.data_ptr(), C.data_ptr(), g.M, g.N, g.ldc, g.ldc, g.strideC, g.strideC, g.batch, 1,
+                                          stream), "transpose(mirror)")
+
+
+def _transpose(src, dst, stream):
+    """dst[b] = src[b]^T for 3-D fp32 tensors whose last axis is contiguous."""
+    nb, r, c = src.shape
+    L.check(L.lib.pylo_b200_transpose(src.data_ptr(), dst.data_ptr(), r, c, src.stride(1), dst.stride(1), src.stride(0),
+                                      dst.stride(0), nb, 0, stream), "transpose")
 
 
 def newton_schulz_eligible(rows: int, cols: int) -> bool:
@@ -102,17 +115,16 @@ def newton_schulz_tc(x: torch.Tensor, coeffs, iters: int = 5, eps: float = 1e-8,
     if stream is None:
         stream = torch.cuda.current_stream().cuda_stream
     c0, c1, c2 = (float(v) for v in coeffs)
-    xt = x.transpose(-2, -1).contiguous()
+    xt = torch.empty((n_b, c, r), dtype=torch.float32, device=x.device)
     a = torch.empty((n_b, r, r), dtype=torch.float32, device=x.device)
     b = torch.empty_like(a)
     x_next = torch.empty_like(x)
     for it in range(iters):
-        _gemm_tn(x, x, a, None, 1.0, 0.0, status, stream)          # a = x x^T
-        _gemm_tn(a, a, b, a, c2, c1, status, stream)               # b = c1 a + c2 a a   (a is symmetric)
-        _gemm_tn(b, xt, x_next, x, 1.0, c0, status, stream)        # x = c0 x + b x
+        _transpose(x, xt, stream)
+        _gemm_tn(x, x, a, None, 1.0, 0.0, status, stream, symmetric=True)     # a = x x^T
+        _gemm_tn(a, a, b, a, c2, c1, status, stream, symmetric=True)          # b = c1 a + c2 a a   (a is symmetric)
+        _gemm_tn(b, xt, x_next, x, 1.0, c0, status, stream)                   # x = c0 x + b x
         x, x_next = x_next, x
-        if it + 1 < iters:
-            xt = x.transpose(-2, -1).contiguous()
     if tall:
         x = x.transpose(-2, -1)
     return x.reshape(shape)

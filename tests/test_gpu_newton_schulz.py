@@ -108,3 +108,35 @@ def test_classes_with_tensor_core_newton_schulz_match_oracle(family):
     got, want, init, opt, _ = _run_both(family, case, 3, [1, 3], hp=hp)
     assert opt.extra_launches > 0, "no matrix took the tensor-core Newton-Schulz"
     _assert_bounds(f"ns_classes[{family}]", got, want, init)
+
+
+@pytest.mark.parametrize("r,k,nb", [(256, 64, 1), (300, 1000, 2), (1000, 36, 1), (4096, 256, 1), (132, 8, 3)])
+def test_symmetric_product_equals_the_full_one(r, k, nb):
+    """x x^T computed on the tiles on and above the diagonal and mirrored must equal the product computed in full,
+    bit for bit above the diagonal and as its exact mirror image below."""
+    from pylo_b200.optim._common import _gemm_tn
+
+    gen = torch.Generator(device="cuda").manual_seed(r + k)
+    x = torch.randn(nb, r, k, device="cuda", generator=gen)
+    d = torch.randn(nb, r, r, device="cuda", generator=gen)
+    d = d + d.transpose(1, 2)
+    s = torch.cuda.current_stream().cuda_stream
+    full = torch.empty(nb, r, r, device="cuda")
+    half = torch.full((nb, r, r), float("nan"), device="cuda")
+    _gemm_tn(x, x, full, d, 2.0, -0.5, None, s)
+    _gemm_tn(x, x, half, d, 2.0, -0.5, None, s, symmetric=True)
+    torch.cuda.synchronize()
+    assert torch.isfinite(half).all()
+    assert torch.equal(torch.triu(half), torch.triu(full))
+    assert torch.equal(half, half.transpose(1, 2))
+
+
+def test_transpose_kernel():
+    from pylo_b200.optim._common import _transpose
+
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    for shape in [(1, 32, 32), (3, 100, 260), (2, 768, 2304), (1, 5, 4100)]:
+        x = torch.randn(shape, device="cuda", generator=gen)
+        out = torch.full((shape[0], shape[2], shape[1]), float("nan"), device="cuda")
+        _transpose(x, out, torch.cuda.current_stream().cuda_stream)
+        assert torch.equal(out, x.transpose(1, 2))
