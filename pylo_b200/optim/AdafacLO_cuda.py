@@ -176,9 +176,13 @@ class AdafacLO_CUDA(_AdafacFamily):
                  hf_key: Optional[str] = "btherien/mulo", network: Optional[MetaMLP] = None,
                  mlp_precision: str = "3xtf32"):
         if isinstance(momentum_dtype, str):
+            if momentum_dtype not in ("float32", "float16", "bfloat16"):
+                raise AssertionError(f"{momentum_dtype} dtype not supported")
             momentum_dtype = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}[momentum_dtype]
-        if momentum_dtype != torch.float32:
-            raise NotImplementedError("AdafacLO_CUDA: the B200 kernels keep momentum in fp32")
+        # Accepted and recorded in the group defaults exactly as the reference does (AdafacLO_cuda.py:109-118,122-135).
+        # The reference class then keeps the momentum in the gradient's dtype all the same: its state is allocated with
+        # p.grad.new_zeros (AdafacLO_cuda.py:256) and the branch that would cast is switched off (AdafacLO_cuda.py:364-373).
+        # So do we: exp_avg is fp32 whatever this argument says, and state_dict() round-trips with the reference.
         if foreach:
             raise NotImplementedError("foreach=True is not implemented (neither is it in the reference)")
         if not torch.cuda.is_available():

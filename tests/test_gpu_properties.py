@@ -226,3 +226,43 @@ def test_elo_celo2_group_step_advances_without_gradients():
         opt.step()
     assert [g["step"] for g in opt.param_groups] == [3, 3]
     assert opt.state_dict()["param_groups"][1]["step"] == 3
+
+
+def test_mulo_cuda_equals_adafaclo_with_the_scaled_groups():
+    """MuLO_CUDA only regroups (MuLO_cuda.py:32-61): stepping it must give what AdafacLO_CUDA gives over groups whose
+    learning rates were divided by the width multipliers by hand."""
+    from pylo_b200 import optim
+
+    class Inf:
+        def __init__(self, n, w):
+            self.n, self.w = n, w
+
+        def ninf(self):
+            return self.n
+
+        def width_mult(self):
+            return self.w
+
+    case = dict(shapes=[(48, 64), (64, 32), (64,)], init_seed=15, init_scale=0.05, grad_seed=16, grad_scale=0.2)
+    mults = [(2, 4.0), (2, 2.0), (1, 1.0)]
+
+    def params():
+        ps = [torch.nn.Parameter(v.cuda()) for v in cases.init_values(case)]
+        for p, (n, w) in zip(ps, mults):
+            p.infshape = Inf(n, w)
+        return ps
+
+    pa, pb = params(), params()
+    mulo = optim.MuLO_CUDA(pa, lr=1e-2, network=_nets("adafaclo"), momentum_dtype="bfloat16")
+    by_hand = optim.AdafacLO_CUDA([{"params": [pb[0]], "lr": 1e-2 / 4.0}, {"params": [pb[1]], "lr": 1e-2 / 2.0},
+                                   {"params": [pb[2]], "lr": 1e-2}], lr=1e-2, network=_nets("adafaclo"))
+    for t in (1, 2):
+        for a, b, g in zip(pa, pb, cases.grads_at(case, t)):
+            a.grad, b.grad = g.cuda(), g.cuda()
+        mulo.step()
+        by_hand.step()
+    for a, b, v in zip(pa, pb, cases.init_values(case)):
+        assert torch.equal(a, b) and not torch.equal(a.detach().cpu(), v)
+    # the momentum stays fp32 whatever momentum_dtype says, as in the reference class (AdafacLO_cuda.py:256,364-373)
+    assert mulo.state[pa[0]]["exp_avg"].dtype == torch.float32
+    assert mulo.defaults["momentum_dtype"] == torch.bfloat16

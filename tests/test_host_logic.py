@@ -130,3 +130,37 @@ def test_apply_items_cover_a_tensor_exactly_once(family, X, Y, tc):
         assert width in (32, 64, 128, 256) and tag & 0xffff == width and rt == 32 * (tag >> 16)
     else:
         assert width == 4 * tag and rt == 16 * (256 // tag)
+
+
+def test_mulo_groups_follow_the_infinite_width_shapes():
+    """MuLO_cuda.py:32-60: matrix-like parameters are grouped by width multiplier with lr / width_mult, the others
+    keep lr; checked on stand-ins for mup's ``infshape`` (the grouping needs nothing else of mup)."""
+    from pylo_b200.optim.MuLO_cuda import mulo_param_groups
+
+    class Inf:
+        def __init__(self, n, w):
+            self.n, self.w = n, w
+
+        def ninf(self):
+            return self.n
+
+        def width_mult(self):
+            return self.w
+
+    def param(shape, n, w):
+        p = torch.nn.Parameter(torch.zeros(shape))
+        p.infshape = Inf(n, w)
+        return p
+
+    a, b, c, d = param((8, 8), 2, 4.0), param((8, 4), 2, 2.0), param((8,), 1, 1.0), param((4, 8), 2, 4.0)
+    groups = mulo_param_groups([a, b, c, d], lr=0.5, weight_decay=0.1)
+    by_lr = {g["lr"]: g["params"] for g in groups}
+    assert set(by_lr) == {0.125, 0.25, 0.5}
+    assert by_lr[0.125] == [a, d] and by_lr[0.25] == [b] and by_lr[0.5] == [c]
+    assert all(g["weight_decay"] == 0.1 for g in groups)
+    two = mulo_param_groups([{"params": [a], "lr": 1.0}, {"params": [c]}], lr=0.5)
+    assert [g["lr"] for g in two if g["params"]] == [0.25, 0.5]
+    with pytest.raises(AssertionError):
+        mulo_param_groups([torch.nn.Parameter(torch.zeros(2, 2))])
+    with pytest.raises(NotImplementedError):
+        mulo_param_groups([param((2, 2, 2), 3, 1.0)])
