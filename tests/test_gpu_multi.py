@@ -262,3 +262,68 @@ def test_two_rank_sharded_step_matches_single_process(family):
     for p in procs:
         p.join(timeout=60)
     assert all(msg == "ok" for _, msg in results), results
+
+
+def _intake_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from pylo_b200 import models, optim
+        from pylo_b200.zero import FusedShardedStep
+
+        shapes = SHAPES + [(72, 48), (300, 260)]
+        case = dict(CASE, shapes=shapes)
+        shard = FusedShardedStep(shapes, dev, init_scale=0.05, seed=4, multicast=False)
+        start = [p.detach().clone() for p in shard.params]
+        shard.attach_grads()
+        torch.manual_seed(0)
+        opt = optim.AdafacLO_CUDA([shard.params[i] for i in shard.owned], lr=1e-2, network=models.MetaMLP(39, 32, 1))
+        torch.manual_seed(0)
+        ref = [torch.nn.Parameter(v.clone()) for v in start]
+        opt1 = optim.AdafacLO_CUDA(ref, lr=1e-2, network=models.MetaMLP(39, 32, 1))
+        same = True
+        for t in (1, 2, 3):
+            # every replica computed its own gradients of ALL tensors (here: seeded per rank and step) ...
+            shard.zero_grads()
+            for p, g in zip(shard.params, cases.grads_at(dict(case, grad_seed=CASE["grad_seed"] + 10 * rank), t)):
+                p.grad.copy_(g.to(dev))
+            # ... the reference answer: all-reduce everything, then every rank would slice out what it owns
+            summed = [p.grad.detach().clone() for p in shard.params]
+            for v in summed:
+                dist.all_reduce(v)
+            shard.reduce_scatter_grads()
+            same = same and all(torch.equal(shard.params[i].grad, summed[i]) for i in shard.owned)
+            opt.step()
+            shard.finish()
+            for p, g in zip(ref, summed):
+                p.grad = g
+            opt1.step()
+        torch.cuda.synchronize()
+        same = same and all(torch.equal(a.detach(), b.detach()) for a, b in zip(shard.params, ref))
+        out.put((rank, "ok" if same else "sharded step fed by the reduce-scatter differs from the all-reduce run"))
+    except Exception:  # pragma: no cover
+        import traceback
+
+        out.put((rank, traceback.format_exc()[-800:]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_reduce_scatter_gradient_intake_is_bit_identical():
+    """Gradients reach their owners by one reduce-scatter over the flat layout; the step that follows equals the
+    step of one process fed with all-reduced gradients, bit for bit."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_intake_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results

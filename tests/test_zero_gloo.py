@@ -42,11 +42,74 @@ def _worker(rank, world, port, out):
         dist.all_reduce(t)
         total = float(sum(p.detach().pow(2).sum() for p in params))
         assert abs(t.item() - total) < 1e-3 * total
+        # gradient intake: every replica has its own gradients of ALL tensors; after the reduce-scatter each rank holds
+        # the sum for the tensors it owns, bit-identical to an all-reduce followed by a slice
+        shard.attach_grads()
+        g = torch.Generator().manual_seed(100 + rank)
+        mine = [torch.randn(sh, generator=g) for sh in SHAPES]
+        for p, v in zip(params, mine):
+            p.grad.copy_(v)                       # what a backward pass would leave
+        summed = [v.clone() for v in mine]
+        for v in summed:
+            dist.all_reduce(v)
+        shard.reduce_scatter_grads()
+        for i in shard.owned:
+            assert torch.equal(params[i].grad, summed[i]), f"gradient of tensor {i} on rank {rank}"
+        shard.zero_grads()
+        assert all(float(p.grad.abs().max()) == 0.0 for p in params)
+        assert all(p.grad.data_ptr() == shard.flat_grad[off:].data_ptr() for p, off in zip(params, shard.offsets))
         out.put((rank, "ok"))
     except Exception as e:  # pragma: no cover
-        out.put((rank, repr(e)))
+        import traceback
+        out.put((rank, traceback.format_exc()[-600:]))
     finally:
         dist.destroy_process_group()
+
+
+def _worker_staged(rank, world, port, out):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from pylo_b200 import zero
+
+        # the [block][rank] layout of the staged step, without its CUDA streams: layout and intake only
+        shard = zero.StagedShardedStep.__new__(zero.StagedShardedStep)
+        shard.pg, shard.world, shard.rank, shard.blocks = None, world, rank, 2
+        shard.owner, shard.block, shard.offsets, shard.subs = zero.partition_blocks(SHAPES, world, 2)
+        shard.base = [sum(shard.subs[:b]) * world for b in range(2)]
+        shard.flat = torch.zeros(sum(shard.subs) * world)
+        shard.params = [torch.nn.Parameter(shard.flat[o:o + zero._numel(sh)].view(sh)) for o, sh in zip(shard.offsets, SHAPES)]
+        shard.owned = [i for i, r in enumerate(shard.owner) if r == rank]
+        shard.attach_grads()
+        g = torch.Generator().manual_seed(200 + rank)
+        mine = [torch.randn(sh, generator=g) for sh in SHAPES]
+        for p, v in zip(shard.params, mine):
+            p.grad.copy_(v)
+        summed = [v.clone() for v in mine]
+        for v in summed:
+            dist.all_reduce(v)
+        shard.reduce_scatter_grads(average=True)
+        for i in shard.owned:
+            assert torch.equal(shard.params[i].grad, summed[i] / world), f"gradient of tensor {i} on rank {rank}"
+        out.put((rank, "ok"))
+    except Exception:  # pragma: no cover
+        import traceback
+        out.put((rank, traceback.format_exc()[-600:]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_staged_layout_gradient_intake_on_two_gloo_ranks():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_staged, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results
 
 
 def test_sharded_step_on_two_gloo_ranks():
