@@ -1103,8 +1103,11 @@ __device__ __forceinline__ uint64_t pk_feature(const PkBase& b) {
 
 #define PK_ROWS 16  // rows per thread in a tile
 
+#ifndef PK_CTAS_VELO
+#define PK_CTAS_VELO 2
+#endif
 template <int FAM>
-__global__ void __launch_bounds__(NT, 2) k_apply_packed(const pylo_tensor_desc* __restrict__ descs,
+__global__ void __launch_bounds__(NT, FAM == PYLO_FAM_VELO ? PK_CTAS_VELO : 2) k_apply_packed(const pylo_tensor_desc* __restrict__ descs,
                                                         const pylo_atile* __restrict__ ctiles, int n_ctiles,
                                                         const pylo_step_params prm) {
   using F = Fam<FAM>;
@@ -1856,7 +1859,7 @@ int pylo_b200_apply_packed(const pylo_tensor_desc* descs, const pylo_atile* ctil
   cudaStream_t s = (cudaStream_t)stream;
   switch (prm->family) {
     case PYLO_FAM_CELO2: k_apply_packed<PYLO_FAM_CELO2><<<grid_for(n_ctiles, 2), NT, 0, s>>>(descs, ctiles, n_ctiles, *prm); break;
-    case PYLO_FAM_VELO: k_apply_packed<PYLO_FAM_VELO><<<grid_for(n_ctiles, 2), NT, 0, s>>>(descs, ctiles, n_ctiles, *prm); break;
+    case PYLO_FAM_VELO: k_apply_packed<PYLO_FAM_VELO><<<grid_for(n_ctiles, PK_CTAS_VELO), NT, 0, s>>>(descs, ctiles, n_ctiles, *prm); break;
     default: return -2;
   }
   return launch_status();
