@@ -135,7 +135,9 @@ __global__ void __launch_bounds__(NS_THREADS, 1) k_gemm_tn_3xtf32(const pylo_gem
   extern __shared__ unsigned char ns_raw[];
   // the tiles need 1024-byte alignment; dynamic shared memory only promises 16
   NsSmem& sm = *reinterpret_cast<NsSmem*>(ns_raw + ((1024 - (smem_addr(ns_raw) & 1023)) & 1023));
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // the warp index as a broadcast from lane 0: the compiler then knows the role branches to be warp-uniform, and
+  // the issuing branch keeps its descriptors and tensor-memory addresses in uniform registers
+  const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
   if (tid == 0) {
     // full: one arrive per loader warp of the stage's group; empty and chunk_ready: one tcgen05.commit;
     // chunk_free: one arrive per epilogue warp
@@ -152,7 +154,7 @@ __global__ void __launch_bounds__(NS_THREADS, 1) k_gemm_tn_3xtf32(const pylo_gem
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = sm.tmem_base;   // columns [0,256): chunk accumulator, [256,512): running sum
+  const uint32_t tmem = __shfl_sync(0xffffffffu, sm.tmem_base, 0);   // columns [0,256): chunk accumulator, [256,512): running sum
   const int tiles_m = (g.M + NS_BM - 1) / NS_BM, tiles_n = (g.N + NS_BN - 1) / NS_BN;
   const int tiles_per_batch = ns_tiles_per_matrix(tiles_m, tiles_n, g.symmetric);
   const long long n_tiles = (long long)tiles_per_batch * g.batch;
@@ -217,8 +219,8 @@ __global__ void __launch_bounds__(NS_THREADS, 1) k_gemm_tn_3xtf32(const pylo_gem
       }
     }
   } else if (warp == NS_EPI_WARPS) {
-    // ------------------------------------------------------------------ the issuing thread
-    if (lane == 0) {
+    // ------------------------------------------------------------------ the issuing thread (one elected lane)
+    if (elect_one()) {
       constexpr uint32_t IDESC = tc_idesc(NS_BN);
       long long kb_count = 0, cc = 0;
       bool dead = false;
