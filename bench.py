@@ -50,7 +50,7 @@ B_BYTES = 40  # state_moments sweep: reads g, p, m(3), v; writes m(3), v
 # from ncu captures of a 4096 x 4096 case, not measured in this run; traffic grows in proportion to the elements
 NCU_TRAFFIC_PER_ELEM = {"k_apply_adafac_cols": 27.58, "k_apply_adafac_tc": 27.44}
 # TF32 / fp16 multiply-adds the tensor-core apply kernels issue per parameter (products x N x K, M = the element)
-TC_ISSUED_FMA_PER_PARAM = {"3xtf32": (3 * 64 + 3 * 32 + 4 * 64 + 4 * 32 + 32) * 8}
+TC_ISSUED_FMA_PER_PARAM = {"3xtf32": (9 + 12 + 1) * 32 * 8}   # 22 products of N = 32, K = 8 per element row
 
 
 def parse(argv=None):
@@ -517,7 +517,7 @@ def measure(args, dev, world, rank, local, headline):
             per_param = TC_ISSUED_FMA_PER_PARAM[args.mlp_precision]
             issued = per_launch_elems * per_param * 2 / (phase_ms[dominant] * 1e-3)
             roofline["tensor"] = {"network_fma_per_param": 1600, "issued_fma_per_param": per_param,
-                                  "operands": "tf32", "products_per_128_params": 15,
+                                  "operands": "tf32", "products_per_128_params": 22,
                                   "issued_tflops": issued / 1e12,
                                   "network_fp32_equiv_tflops": per_launch_elems * 3200 / (phase_ms[dominant] * 1e-3) / 1e12}
         elif args.optimizer in ("adafaclo", "elo") and dominant in ("k_apply", "k_apply_adafac_cols") and clocks and clocks.get("sm_mhz"):

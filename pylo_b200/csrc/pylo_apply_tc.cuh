@@ -11,40 +11,42 @@
 //     elements of the tile, so together with the first-layer bias they are a per-row bias vector: it is read from
 //     the table k_prep_apply makes (desc.h_a, 32 floats per row) and enters the product through operand B, as two
 //     rows (its high and low part) that meet two constant-1 columns of operand A.  First layer: K = 24;
-//   * fp32 accuracy is kept by splitting every operand into a TF32 high part and a TF32 low part.  Of the three
-//     products per layer that this needs (hi x hi, hi x lo, lo x hi) the two that share operand A run as ONE
-//     product of twice the width: operand B holds [B_hi | B_lo] stacked along N (N = 64), so the accumulator has
-//     64 columns, hi x hi in the first 32 and hi x lo in the last 32, and A_lo x B_hi accumulates into the first
-//     32.  The two halves are added when the accumulator is read back.  An instruction of width 64 costs the tensor
-//     pipe the same issue slot as one of width 32, so a tile takes 6 + 9 = 15 products instead of 25;
+//   * fp32 accuracy is kept by splitting every operand into a TF32 high part and a TF32 low part and running
+//     three products per layer and K step (hi x hi, hi x lo, lo x hi) into one accumulator of 32 columns.  Operand
+//     B holds the high parts in rows 0..31 and the low parts in rows 32..63 of one block; a product addresses
+//     either half through its descriptor's start address.  A tile takes 9 + 13 = 22 products of width 32;
 //   * the second-layer bias is one more product, of a constant operand A (ones, in shared memory) with a block of
 //     operand B that holds the bias's high and low parts;
 //   * relu, the split of the hidden activations, the two output heads and the parameter update stay on the CUDA
-//     cores, which work on one warpgroup's tile while the tensor core works on another's: four warpgroups per
+//     cores, which work on one warpgroup's tile while the tensor core works on another's: five warpgroups per
 //     CTA, one CTA per SM; every warpgroup is an independent worker with its own work items, its own copy of the
-//     weights in shared memory, its own 128 tensor-memory columns (64 operand A + 64 accumulator) and its own
-//     barriers, so the warpgroups drift apart instead of marching in step.
+//     weights in shared memory, its own 96 tensor-memory columns (32 operand A high parts, 32 low parts, 32
+//     accumulator) and its own barriers, so the warpgroups drift apart instead of marching in step;
+//   * the products are issued by one elected lane inside a warp-uniform branch (the warp index is a broadcast
+//     from lane 0), so that their descriptors and tensor-memory addresses live in uniform registers: issued from
+//     a branch on the thread index, each product cost its thread ~52 cycles; this way ~24.
 // Every wait on the tensor core is bounded.  A thread whose wait ran out records it in *status, stops waiting
 // and stops storing (its parameters, and their copies on the peers, keep their old values), and goes on to
 // the end, where the kernel frees its tensor memory.  A launch that finds *status already set stores nothing.
 #pragma once
 
 #ifndef TC_WGS
-#define TC_WGS 4                 // warpgroups per CTA: 4 x 128 tensor-memory columns are the SM's 512
+#define TC_WGS 5                 // warpgroups per CTA: 5 x 96 of the SM's 512 tensor-memory columns
 #endif
 #define TC_NT (TC_WGS * 128)
 #ifndef TC_BOUND_THREADS
 #define TC_BOUND_THREADS TC_NT   // a larger bound lowers the register cap (65536 / bound): room for a co-resident kernel
 #endif
 #define TC_COLS 128              // tensor columns per work item: one per lane of the accumulator tile
-#define TC_WG_TMEM 128           // tensor-memory columns per warpgroup: [0,64) operand A, [64,128) accumulator
+#define TC_WG_TMEM 96            // tensor-memory columns per warpgroup: [0,32) operand A high parts, [32,64) low parts, [64,96) accumulator
 #define TC_K1 24                 // first-layer K: 16 element-wise + 6 column features + 2 constant columns
 #define TC_SPIN_LIMIT (1 << 20)
 #ifndef TC_POLL_SLEEP_NS
 #define TC_POLL_SLEEP_NS 40
 #endif
 #define TC_LBO 512               // bytes between 16-byte K chunks of a 32-row operand B (32 rows x 16 bytes)
-#define TC_LBO64 1024            // the same for a 64-row (stacked) operand B
+#define TC_LBO64 1024            // the same for a 64-row operand B (high parts in rows 0..31, low parts in rows 32..63)
+#define TC_LOW_HALF ((4 * TC_SBO) >> 4)   // descriptor start-address offset (16-byte units) of rows 32..63
 #define TC_SBO 128               // bytes between groups of eight rows
 #define TC_ONES_BYTES 2304       // constant operand A: every 16-byte chunk is (1, 1, 0, 0)
 
@@ -133,7 +135,6 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t saddr, int lbo = TC_LBO, in
 // instruction descriptor: fp32 accumulate, TF32 x TF32, both operands K-major, M = 128, N = 32 or 64
 __host__ __device__ constexpr uint32_t tc_idesc(uint32_t n) { return (1u << 4) | (2u << 7) | (2u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
 constexpr uint32_t TC_IDESC = tc_idesc(32);
-constexpr uint32_t TC_IDESC64 = tc_idesc(64);
 
 // read-only 128-bit load issued where it is written (the compiler would otherwise sink it to its first use)
 __device__ __forceinline__ float4 ldg4_early(const float* p) {
@@ -161,7 +162,7 @@ __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__flo
 struct __align__(128) TcWgSmem {
   float b1[64 * TC_K1];   // first layer, rows 0..31 the high parts, 32..63 the low parts; K = 24 (K rows 22 and 23 of
                           // the high half are rewritten for every tensor row: the row's bias vector, high and low part)
-  float b2[64 * 32];      // second layer, stacked the same way; K = 32
+  float b2[64 * 32];      // second layer, laid out the same way; K = 32
   float b2bias[32 * 8];   // second-layer bias as a K = 8 block: (high part, low part, 0 ...)
   float w3[64 + 4];       // output layer, pair-major (Fold::W3P), then its two biases
   uint64_t bar;
@@ -202,7 +203,7 @@ __global__ void __launch_bounds__(TC_BOUND_THREADS, 1) k_apply_adafac_tc(const p
   const uint32_t t_wg = __shfl_sync(0xffffffffu, smem.tmem_base, 0) + wg * TC_WG_TMEM;   // lane 0 of this warpgroup's columns
   const uint32_t t_lane = t_wg + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes
   const uint32_t tA = t_lane, tD = t_lane + 64;
-  constexpr uint64_t KSTEP64 = (2 * TC_LBO64) >> 4;  // one product consumes two K chunks of the stacked operand
+  constexpr uint64_t KSTEP64 = (2 * TC_LBO64) >> 4;  // one product consumes two K chunks of operand B
   // every row of the constant operand is (1, 1, 0, 0, ...): any in-range chunk of the buffer holds that pattern
   const uint64_t desc_ones = tc_desc(smem_addr(smem.ones), 128, 128);
   uint32_t parity = 0;
@@ -320,8 +321,8 @@ __global__ void __launch_bounds__(TC_BOUND_THREADS, 1) k_apply_adafac_tc(const p
         TC_CLK(10)  // features and split
         tc_st16(tA, hi);
         tc_st8(tA + 16, chi);
-        tc_st16(tA + 24, lo);
-        tc_st8(tA + 40, clo);
+        tc_st16(tA + 32, lo);
+        tc_st8(tA + 48, clo);
       }
       // the next row's operands: requested now that this row's are consumed (only p is still needed, for the
       // update), so the two sets never share the register file; they land during the two products.  (Requesting
@@ -338,9 +339,12 @@ __global__ void __launch_bounds__(TC_BOUND_THREADS, 1) k_apply_adafac_tc(const p
           tc_fence_after();
           const uint64_t desc_b1 = tc_desc(smem_addr(sm.b1), TC_LBO64);
 #pragma unroll
-          for (int s = 0; s < 3; ++s) tc_mma(t_wg + 64, t_wg + 8 * s, desc_b1 + s * KSTEP64, TC_IDESC64, s > 0);   // hi x [hi | lo]
+          for (int s = 0; s < 3; ++s) {
+            tc_mma(t_wg + 64, t_wg + 32 + 8 * s, desc_b1 + s * KSTEP64, TC_IDESC, s > 0);          // lo x hi
+            tc_mma(t_wg + 64, t_wg + 8 * s, desc_b1 + TC_LOW_HALF + s * KSTEP64, TC_IDESC, 1);     // hi x lo
+          }
 #pragma unroll
-          for (int s = 0; s < 3; ++s) tc_mma(t_wg + 64, t_wg + 24 + 8 * s, desc_b1 + s * KSTEP64, TC_IDESC, 1);    // lo x hi
+          for (int s = 0; s < 3; ++s) tc_mma(t_wg + 64, t_wg + 8 * s, desc_b1 + s * KSTEP64, TC_IDESC, 1);   // hi x hi
           tc_commit(&sm.bar);
         }
         __syncwarp();
@@ -349,31 +353,26 @@ __global__ void __launch_bounds__(TC_BOUND_THREADS, 1) k_apply_adafac_tc(const p
       parity ^= 1;
       tc_fence_after();
       TC_CLK(2)  // first-layer products: issue + wait
-      // ---- hidden layer 1: add the accumulator's halves, relu, split, back into tensor memory as operand A
+      // ---- hidden layer 1: relu, split, back into tensor memory as operand A
       {
-        uint32_t d0[16], d1[16], e0[16], e1[16];
+        uint32_t d0[16], d1[16];
         tc_ld16(tD, d0);        // everything is requested before anything is touched: one load latency
-        tc_ld16(tD + 32, d1);
-        tc_ld16(tD + 16, e0);
-        tc_ld16(tD + 48, e1);
+        tc_ld16(tD + 16, d1);
         tc_wait_ld();
         TC_CLK(3)  // accumulator read-back
-        auto split_store = [&](const uint32_t (&a)[16], const uint32_t (&b)[16], int half) {
+        auto split_store = [&](const uint32_t (&a)[16], int half) {
           uint32_t hi[16], lo[16];
 #pragma unroll
-          for (int k = 0; k < 16; k += 2) {
-            float s0, s1;
-            unpack2(add2(pack2(__uint_as_float(a[k]), __uint_as_float(a[k + 1])), pack2(__uint_as_float(b[k]), __uint_as_float(b[k + 1]))), s0, s1);
-            s0 = fmaxf(s0, 0.f); s1 = fmaxf(s1, 0.f);
-            const float h0 = tf32_hi(s0), h1 = tf32_hi(s1);
-            hi[k] = __float_as_uint(h0); hi[k + 1] = __float_as_uint(h1);
-            lo[k] = __float_as_uint(s0 - h0); lo[k + 1] = __float_as_uint(s1 - h1);
+          for (int k = 0; k < 16; ++k) {
+            const float v = fmaxf(__uint_as_float(a[k]), 0.f), h = tf32_hi(v);
+            hi[k] = __float_as_uint(h);
+            lo[k] = __float_as_uint(v - h);
           }
           tc_st16(tA + 16 * half, hi);
           tc_st16(tA + 32 + 16 * half, lo);
         };
-        split_store(d0, d1, 0);
-        split_store(e0, e1, 1);
+        split_store(d0, 0);
+        split_store(d1, 1);
       }
       TC_CLK(4)  // relu, split, stores issued
       tc_wait_st();
@@ -386,10 +385,13 @@ __global__ void __launch_bounds__(TC_BOUND_THREADS, 1) k_apply_adafac_tc(const p
           const uint64_t desc_b2 = tc_desc(smem_addr(sm.b2), TC_LBO64);
           const uint64_t desc_b2bias = tc_desc(smem_addr(sm.b2bias));
 #pragma unroll
-          for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 8 * s, desc_b2 + s * KSTEP64, TC_IDESC64, s > 0);   // hi x [hi | lo]
+          for (int s = 0; s < 4; ++s) {
+            tc_mma(t_wg + 64, t_wg + 32 + 8 * s, desc_b2 + s * KSTEP64, TC_IDESC, s > 0);          // lo x hi
+            tc_mma(t_wg + 64, t_wg + 8 * s, desc_b2 + TC_LOW_HALF + s * KSTEP64, TC_IDESC, 1);     // hi x lo
+          }
 #pragma unroll
-          for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 32 + 8 * s, desc_b2 + s * KSTEP64, TC_IDESC, 1);    // lo x hi
-          tc_mma_ss(t_wg + 64, desc_ones, desc_b2bias, TC_IDESC, 1);                                               // bias
+          for (int s = 0; s < 4; ++s) tc_mma(t_wg + 64, t_wg + 8 * s, desc_b2 + s * KSTEP64, TC_IDESC, 1);   // hi x hi
+          tc_mma_ss(t_wg + 64, desc_ones, desc_b2bias, TC_IDESC, 1);                                         // bias
           tc_commit(&sm.bar);
         }
         __syncwarp();
@@ -398,30 +400,25 @@ __global__ void __launch_bounds__(TC_BOUND_THREADS, 1) k_apply_adafac_tc(const p
       parity ^= 1;
       tc_fence_after();
       TC_CLK(5)  // second-layer products: issue + wait
-      // ---- hidden layer 2 (halves added, relu) and the two output heads as packed dot products over unit pairs
+      // ---- hidden layer 2 (relu) and the two output heads as packed dot products over unit pairs
       uint64_t od[2] = {0ull, 0ull}, om[2] = {0ull, 0ull};
       {
-        uint32_t d0[16], d1[16], e0[16], e1[16];
+        uint32_t d0[16], d1[16];
         tc_ld16(tD, d0);
-        tc_ld16(tD + 32, d1);
-        tc_ld16(tD + 16, e0);
-        tc_ld16(tD + 48, e1);
+        tc_ld16(tD + 16, d1);
         tc_wait_ld();
         TC_CLK(3)
-        auto heads = [&](const uint32_t (&a)[16], const uint32_t (&b)[16], int half) {
+        auto heads = [&](const uint32_t (&a)[16], int half) {
 #pragma unroll
           for (int jp = 0; jp < 8; ++jp) {
             const ulonglong2 w = *reinterpret_cast<const ulonglong2*>(&sm.w3[4 * (half * 8 + jp)]);  // (dir pair, mag pair)
-            float s0, s1;
-            unpack2(add2(pack2(__uint_as_float(a[2 * jp]), __uint_as_float(a[2 * jp + 1])),
-                         pack2(__uint_as_float(b[2 * jp]), __uint_as_float(b[2 * jp + 1]))), s0, s1);
-            const uint64_t r = pack2(fmaxf(s0, 0.f), fmaxf(s1, 0.f));
+            const uint64_t r = pack2(fmaxf(__uint_as_float(a[2 * jp]), 0.f), fmaxf(__uint_as_float(a[2 * jp + 1]), 0.f));
             od[jp & 1] = fma2(w.x, r, od[jp & 1]);
             om[jp & 1] = fma2(w.y, r, om[jp & 1]);
           }
         };
-        heads(d0, d1, 0);
-        heads(e0, e1, 1);
+        heads(d0, 0);
+        heads(d1, 1);
       }
       {
         float a, b, c, dd;

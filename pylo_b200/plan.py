@@ -311,7 +311,7 @@ class LoPlan:
         else:
             self.apply_kernel = "k_apply_packed<CELO2>" if family == L.FAM_CELO2 else "k_apply_packed<VELO>"
         #: device flag the tensor-core kernel raises when one of its bounded waits ran out
-        self.status = torch.zeros(64, dtype=torch.int32, device=self.device) if self.tensor_cores else None
+        self.status = torch.zeros(128, dtype=torch.int32, device=self.device) if self.tensor_cores else None
         # a pinned copy of the flag follows every launch without blocking; the next launch looks at it once it landed
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory() if self.tensor_cores else None
         self._status_event = None
