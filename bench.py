@@ -25,6 +25,7 @@ it does not load the CUDA library of this package.
 
 import argparse
 import copy
+import datetime
 import gc
 import json
 import os
@@ -70,9 +71,10 @@ def parse(argv=None):
                     help="adafaclo / elo: the network's hidden layers as scalar fp32 FMAs, or as tensor-core products of "
                          "operands split into two TF32 parts (fp32-faithful: hi x hi + hi x lo + lo x hi)")
     ap.add_argument("--blocks", type=int, default=8, help="N>1: stages whose parameter all-gathers overlap the next stage")
-    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "staged"],
-                    help="N>1: how updated parameters reach the other ranks (peer stores fused into the apply kernels, "
-                         "or NCCL all-gathers per block)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "copy", "staged"],
+                    help="N>1: how updated parameters reach the other ranks (fused: peer stores from the apply kernels; "
+                         "copy: one device-to-device copy per param group and peer on side streams; staged: NCCL "
+                         "all-gathers per block)")
     ap.add_argument("--no-multicast", action="store_true",
                     help="N>1, fused exchange: one store per peer instead of one multimem store through the switch")
     ap.add_argument("--no-e2e", action="store_true")
@@ -298,6 +300,17 @@ def replica_checksum(flat):
     return torch.stack([s1, s2])
 
 
+def ranks_agree(ok, world, dev):
+    """True if ``ok`` holds on every rank (one tiny all-reduce; at one rank just ``ok``)."""
+    if world == 1:
+        return bool(ok)
+    import torch.distributed as dist
+
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(int(flag.item()))
+
+
 def measure(args, dev, world, rank, local, headline):
     """One configuration on the current process group: returns the JSON line (rank 0) or None."""
     import torch.distributed as dist
@@ -316,8 +329,13 @@ def measure(args, dev, world, rank, local, headline):
     free, _ = torch.cuda.mem_get_info()
     state_bytes = 16 if args.optimizer not in ("celo2", "elo_celo2") else 20
     need = total * 4 + (total / world) * (state_bytes + 1) * 1.02 + 4e9
+    why = None
     if need > free * 0.97:
-        raise MemoryError(f"workload needs ~{need / 1e9:.0f} GB per GPU, {free / 1e9:.0f} GB free: refusing to run")
+        why = f"workload needs ~{need / 1e9:.0f} GB per GPU, {free / 1e9:.0f} GB free: refusing to run"
+    # the ranks decide together: one rank that skipped a configuration while the others ran its collectives would
+    # leave them waiting for it
+    if not ranks_agree(why is None, world, dev):
+        raise MemoryError(why or "another rank has too little free memory for this workload: refusing to run")
 
     exchange = args.exchange
     if exchange == "auto":
@@ -325,11 +343,12 @@ def measure(args, dev, world, rank, local, headline):
     if world == 1:
         exchange = "none"
     shard = None
-    if exchange == "fused" or (world == 1 and args.optimizer in ("adafaclo", "elo")):
+    if exchange in ("fused", "copy") or (world == 1 and args.optimizer in ("adafaclo", "elo")):
         # N>1: parameters reach the other ranks as peer stores from the apply kernels; N=1: plain flat buffer
         ok, why = 1, ""
         try:
-            shard = FusedShardedStep(shapes, dev, init_scale=0.02, seed=1, multicast=False if args.no_multicast else None)
+            shard = FusedShardedStep(shapes, dev, init_scale=0.02, seed=1, multicast=False if args.no_multicast else None,
+                                     push="copies" if exchange == "copy" else "stores")
         except Exception as e:  # symmetric memory unavailable on this box: fall back to NCCL gathers
             ok, why = 0, repr(e)
         if world > 1:
@@ -349,13 +368,21 @@ def measure(args, dev, world, rank, local, headline):
         shard = StagedShardedStep(shapes, dev, blocks=min(args.blocks, 4), init_scale=0.02, seed=1)
     if exchange == "fused" and getattr(shard, "multicast_base", 0):
         exchange = "fused-multicast"
+    if exchange == "copy":
+        exchange = "copies-per-group"
     args.exchange_used = exchange
     owned = shard.owned
     params = [shard.params[i] for i in owned]
-    pool = W.make_grad_pool([shapes[i] for i in owned], gscale, dev, seed=2 + rank, kind=gkind)
-    for p in params:
-        p.grad = pool[tuple(p.shape)]
-    opt = build_optimizer(args, shard, params)
+    why = None
+    try:
+        pool = W.make_grad_pool([shapes[i] for i in owned], gscale, dev, seed=2 + rank, kind=gkind)
+        for p in params:
+            p.grad = pool[tuple(p.shape)]
+        opt = build_optimizer(args, shard, params)
+    except Exception as e:
+        why = f"{type(e).__name__}: {e}"
+    if not ranks_agree(why is None, world, dev):
+        raise RuntimeError(why or "another rank could not set this configuration up")
     owned_n = sum(p.numel() for p in params)
     velo = args.optimizer == "velo"
     loss = torch.tensor(1.0, device=dev)
@@ -582,7 +609,9 @@ def run_b200(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # a short limit: the longest step of any configuration here takes seconds; if ranks ever disagree on the
+        # order of collectives the run should end, not sit out the default ten minutes on eight GPUs
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     try:
         line, ok = measure(args, dev, world, rank, local, headline=True)
     except MemoryError as e:

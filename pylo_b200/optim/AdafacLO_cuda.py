@@ -237,6 +237,10 @@ class AdafacLO_CUDA(_AdafacFamily):
                     torch.nn.utils.clip_grad_norm_(p, group["max_grad_norm"])  # per tensor, as AdafacLO_cuda.py:214-215
             plist = [p for p in group["params"] if p.grad is not None]
             if not plist:
+                # a sharded step hangs collectives on this hook: every rank must reach it for every group, in order,
+                # also a rank that owns nothing of the group
+                if self.after_group is not None:
+                    self.after_group(gi)
                 continue
             if any(p.grad.is_sparse for p in plist):
                 raise RuntimeError("Sparse gradients not supported")
@@ -298,6 +302,10 @@ class ELO_CUDA(_AdafacFamily):
         for gi, group in enumerate(self.param_groups):
             plist = [p for p in group["params"] if p.grad is not None]
             if not plist:
+                # a sharded step hangs collectives on this hook: every rank must reach it for every group, in order,
+                # also a rank that owns nothing of the group
+                if self.after_group is not None:
+                    self.after_group(gi)
                 continue
             if any(p.grad.is_sparse for p in plist):
                 raise RuntimeError("Sparse gradients not supported")

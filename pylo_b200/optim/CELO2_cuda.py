@@ -214,6 +214,10 @@ class _Celo2Family(Optimizer):
                 group["step"] = group.get("step", 0) + 1
             plist = [p for p in group["params"] if p.grad is not None]
             if not plist:
+                # a sharded step hangs collectives on this hook: every rank must reach it for every group, in order,
+                # also a rank that owns nothing of the group
+                if self.after_group is not None:
+                    self.after_group(gi)
                 continue
             sig = tuple((p.data_ptr(), bool(group["is_embedding"]), bool(group["use_adamw_for_1d"])) for p in plist)
             cached = self._plans.get(gi)

@@ -443,6 +443,11 @@ class GradNorm:
     """Device-side sum of squares of a list of gradients (the global-norm clip)."""
 
     def __init__(self, sizes: Sequence[int], device):
+        self.out = torch.zeros(1, dtype=torch.float32, device=device)
+        self._keepalive = []
+        self.n_tiles = 0
+        if len(sizes) == 0:   # a rank that owns no tensor still takes part in the all-reduce of the sum: with zero
+            return
         self.items = np.zeros(len(sizes), dtype=L.GVEC_DTYPE)
         self.items["n"] = sizes
         tiles, _ = make_tiles(sizes)
@@ -450,11 +455,12 @@ class GradNorm:
         self.n_tiles = len(tiles)
         self.table = DeviceTable(self.items, device)
         self.scratch = torch.zeros(max(self.n_tiles, 1), dtype=torch.float32, device=device)
-        self.out = torch.zeros(1, dtype=torch.float32, device=device)
-        self._keepalive = []
 
     def run(self, grads: Sequence[torch.Tensor], stream: int):
         self._keepalive = []
+        if self.n_tiles == 0:
+            self.out.zero_()
+            return self.out
         for i, g in enumerate(grads):
             if not (g.dtype == torch.float32 and g.is_contiguous()):
                 g = g.to(torch.float32).contiguous()

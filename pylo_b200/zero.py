@@ -223,7 +223,7 @@ def split_in_groups(params, groups: int):
         if len(out) < groups - 1 and acc >= total * (len(out) + 1) / groups:
             out.append({"params": cur})
             cur = []
-    if cur:
+    if cur or not out:   # a rank that owns nothing still gets one (empty) group: its hooks must run
         out.append({"params": cur})
     return out
 
@@ -242,10 +242,18 @@ class FusedShardedStep(_GradIntake):
     """
 
     def __init__(self, shapes: Sequence[Tuple[int, ...]], device, init_scale: float = 0.02, seed: int = 1,
-                 process_group=None, cost=None, multicast: Optional[bool] = None):
+                 process_group=None, cost=None, multicast: Optional[bool] = None, push: str = "stores"):
         """``multicast``: reach the peers through the NVLink switch's multicast mapping of the buffer (one
         ``multimem`` store per value, replicated by the switch) instead of one store per peer.  None: use it
-        where the symmetric memory offers a multicast address, True: require it, False: never."""
+        where the symmetric memory offers a multicast address, True: require it, False: never.
+
+        ``push``: "stores" (the apply kernels store into the peers' buffers themselves) or "copies": the kernels
+        store locally only, and once a param group's kernels are enqueued (:meth:`after_group`) the range of the
+        buffer that group owns is copied into every peer's buffer with one device-to-device copy per peer, each
+        on a stream of its own.  Those copies are the driver's (copy engines, no SMs) and keep NVLink busy while
+        the next groups' sweeps - all of them, not only the apply sweeps - run."""
+        if push not in ("stores", "copies"):
+            raise ValueError("push must be 'stores' or 'copies'")
         self.pg = process_group
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
@@ -277,7 +285,13 @@ class FusedShardedStep(_GradIntake):
             view.normal_(0.0, init_scale, generator=gen)
             self.params.append(torch.nn.Parameter(view, requires_grad=True))
         self.owned = [i for i, r in enumerate(self.owner) if r == self.rank]
-        for i in self.owned:  # where this tensor lives in every other rank's buffer
+        self.push = push if self.world > 1 else "stores"
+        self._group_ranges, self._pushed = [], False
+        if self.push == "copies":
+            peers = [r for r in range(self.world) if r != self.rank]
+            self._peer_flat = [self.handle.get_buffer(r, (n,), torch.float32) for r in peers]
+            self._copy_streams = [torch.cuda.Stream(device=device) for _ in peers]
+        for i in self.owned if self.push == "stores" else []:  # where this tensor lives in every other rank's buffer
             if self.multicast_base:
                 self.params[i]._pylo_peer_ptrs = [self.multicast_base + 4 * self.offsets[i]]
                 self.params[i]._pylo_peer_multicast = True
@@ -288,14 +302,45 @@ class FusedShardedStep(_GradIntake):
     def param_groups(self, is_embedding=None, groups: int = 1):
         """The owned tensors as ``groups`` param groups of similar size, in buffer order (the optimizer
         runs its param groups one after the other, which lets a caller pipeline gradient arrival)."""
-        return split_in_groups([self.params[i] for i in self.owned], groups)
+        out = split_in_groups([self.params[i] for i in self.owned], groups)
+        index_of = {id(self.params[i]): i for i in self.owned}
+        self._group_ranges = []
+        for g in out:  # a group's tensors are consecutive in the owner's region: one contiguous range
+            idx = [index_of[id(p)] for p in g["params"]]
+            self._group_ranges.append((min(self.offsets[i] for i in idx), max(self.offsets[i] + self.params[i].numel() for i in idx)))
+        return out
+
+    def _push_range(self, a: int, b: int):
+        ev = torch.cuda.Event()
+        ev.record()
+        src = self.flat[a:b]
+        for dst, stream in zip(self._peer_flat, self._copy_streams):
+            with torch.cuda.stream(stream):
+                stream.wait_event(ev)
+                dst[a:b].copy_(src, non_blocking=True)
+        self._pushed = True
 
     def after_group(self, gi: int):
-        return None
+        """Hook for the optimizer: param group ``gi`` is enqueued.  With ``push="copies"`` its range starts
+        travelling to the peers now."""
+        if self.push == "copies" and gi < len(self._group_ranges):
+            self._push_range(*self._group_ranges[gi])
 
     def finish(self):
-        """Order the peers' stores before the next read of the parameters (one tiny all-reduce)."""
+        """Order the peers' writes before the next read of the parameters: with ``push="copies"`` join the copy
+        streams (pushing the whole owned region first if no hook ran this step), then one tiny all-reduce - a rank's
+        contribution to it is enqueued behind its own stores or copies, so its completion here means every peer is
+        done writing into this rank's buffer."""
         if self.world > 1:
+            if self.push == "copies":
+                if not self._pushed and self.owned:
+                    a = min(self.offsets[i] for i in self.owned)
+                    b = max(self.offsets[i] + self.params[i].numel() for i in self.owned)
+                    self._push_range(a, b)
+                cur = torch.cuda.current_stream()
+                for stream in self._copy_streams:
+                    cur.wait_stream(stream)
+                self._pushed = False
             dist.all_reduce(self._token, group=self.pg)
 
     gather = finish
@@ -347,7 +392,10 @@ class StagedShardedStep(_GradIntake):
             else:
                 parts = [({}, [p for p in mine if not is_embedding(tuple(p.shape))]),
                          ({"is_embedding": True}, [p for p in mine if is_embedding(tuple(p.shape))])]
-            parts = [(extra, ps) for extra, ps in parts if ps]
+            # empty parts are dropped, but every rank keeps at least one group per block - empty if it owns nothing
+            # there - because the group that closes a block starts the block's all-gather, and all ranks must start
+            # the same gathers in the same order
+            parts = [(extra, ps) for extra, ps in parts if ps] or [({}, [])]
             for k, (extra, ps) in enumerate(parts):
                 out.append(dict(params=ps, **extra))
                 info.append((b, k == len(parts) - 1))

@@ -1,6 +1,7 @@
 """Two ranks on two GPUs: the sharded step (whole-tensor ownership + parameter all-gather) gives the same
 parameters as one process that owns everything.  Skipped when fewer than two GPUs are visible."""
 
+import datetime
 import os
 import socket
 
@@ -10,6 +11,9 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 import cases
+
+# ranks that disagree on the order of collectives should end the test, not sit out the default ten minutes
+PG_TIMEOUT = datetime.timedelta(seconds=90)
 
 pytestmark = pytest.mark.gpu
 
@@ -49,7 +53,7 @@ def _worker(rank, world, port, family, out):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=PG_TIMEOUT)
     try:
         from pylo_b200.zero import ShardedStep
 
@@ -84,23 +88,31 @@ def _worker(rank, world, port, family, out):
         dist.destroy_process_group()
 
 
-def _staged_worker(rank, world, port, out):
+def _staged_worker(rank, world, port, out, lone_tensor=None):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=PG_TIMEOUT)
     try:
         from pylo_b200 import models, optim
         from pylo_b200.zero import StagedShardedStep
 
-        shapes = SHAPES + [(72, 48), (48, 72), (30, 200)]
+        # lone_tensor: a single tensor, so that the second rank owns nothing and still has to start every gather
+        shapes = [(72, 48)] if lone_tensor else SHAPES + [(72, 48), (48, 72), (30, 200)]
         case = dict(CASE, shapes=shapes)
         shard = StagedShardedStep(shapes, dev, blocks=3, init_scale=0.05, seed=4)
         start = [p.detach().clone() for p in shard.params]
-        torch.manual_seed(0)
-        opt = optim.AdafacLO_CUDA(shard.param_groups(), lr=1e-2, network=models.MetaMLP(39, 32, 1))
+
+        def make(params):
+            torch.manual_seed(0)
+            if lone_tensor == "celo2":
+                return optim.CELO2_CUDA(params, lr=1e-2, clip_grad=True, network=models.CELO2MLP())
+            return optim.AdafacLO_CUDA(params, lr=1e-2, network=models.MetaMLP(39, 32, 1))
+
+        opt = make(shard.param_groups())
         opt.after_group = shard.after_group
+        opt._sharded = True
         for t in (1, 2, 3):
             grads = cases.grads_at(case, t)
             for i in shard.owned:
@@ -109,8 +121,7 @@ def _staged_worker(rank, world, port, out):
             shard.finish()
         torch.cuda.synchronize()
         ref = [torch.nn.Parameter(v.clone()) for v in start]
-        torch.manual_seed(0)
-        opt1 = optim.AdafacLO_CUDA(ref, lr=1e-2, network=models.MetaMLP(39, 32, 1))
+        opt1 = make(ref)
         for t in (1, 2, 3):
             for p, g in zip(ref, cases.grads_at(case, t)):
                 p.grad = g.to(dev)
@@ -127,19 +138,19 @@ def _staged_worker(rank, world, port, out):
         dist.destroy_process_group()
 
 
-def _fused_worker(rank, world, port, family, out, multicast=False):
+def _fused_worker(rank, world, port, family, out, multicast=False, push="stores"):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=PG_TIMEOUT)
     try:
         from pylo_b200 import models, optim
         from pylo_b200.zero import FusedShardedStep
 
         shapes = SHAPES + [(72, 48), (300, 260)]
         case = dict(CASE, shapes=shapes)
-        shard = FusedShardedStep(shapes, dev, init_scale=0.05, seed=4, multicast=multicast)
+        shard = FusedShardedStep(shapes, dev, init_scale=0.05, seed=4, multicast=multicast, push=push)
         if multicast is None and not shard.multicast_base:
             out.put((rank, "no-multicast"))
             return
@@ -158,7 +169,11 @@ def _fused_worker(rank, world, port, family, out, multicast=False):
             kw = dict(all_shapes=shapes, owned=shard.owned) if sharded else {}
             return optim.VeLO_CUDA(params, lr=10.0, num_steps=100, rnn=rnn, mlp=mlp, **kw)
 
-        opt = make([shard.params[i] for i in shard.owned], True)
+        if push == "copies" and family == "adafaclo":   # two param groups: each one's range leaves when it is enqueued
+            opt = make(shard.param_groups(groups=2), True)
+            opt.after_group = shard.after_group
+        else:                                            # no hook: finish() pushes the whole owned region
+            opt = make([shard.params[i] for i in shard.owned], True)
         for t in (1, 2, 3):
             grads = cases.grads_at(case, t)
             for i in shard.owned:
@@ -215,6 +230,23 @@ def test_two_rank_fused_exchange_is_bit_identical(family):
 
 
 @pytest.mark.parametrize("family", ["adafaclo", "velo"])
+def test_two_rank_copy_pushed_exchange_is_bit_identical(family):
+    """The kernels store locally; every param group's range is copied into the peer's buffer on a side stream."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_fused_worker, args=(r, 2, port, family, out, False, "copies")) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results
+
+
+@pytest.mark.parametrize("family", ["adafaclo", "velo"])
 def test_two_rank_fused_multicast_exchange_is_bit_identical(family):
     """The same through the NVLink switch's multicast mapping of the buffer: one multimem store per value."""
     if torch.cuda.device_count() < 2:
@@ -248,6 +280,24 @@ def test_two_rank_staged_step_with_overlapped_gathers_is_bit_identical():
     assert all(msg == "ok" for _, msg in results), results
 
 
+@pytest.mark.parametrize("family", ["adafaclo", "celo2"])
+def test_rank_that_owns_nothing_still_takes_part(family):
+    """One tensor, two ranks: the second rank's optimizer has only empty param groups, and must still start every
+    block's all-gather (and the all-reduce of the gradient norm) in the same order as the first."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_staged_worker, args=(r, 2, port, out, family)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results
+
+
 @pytest.mark.parametrize("family", ["adafaclo", "elo_celo2", "velo"])
 def test_two_rank_sharded_step_matches_single_process(family):
     if torch.cuda.device_count() < 2:
@@ -269,7 +319,7 @@ def _intake_worker(rank, world, port, out):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=PG_TIMEOUT)
     try:
         from pylo_b200 import models, optim
         from pylo_b200.zero import FusedShardedStep

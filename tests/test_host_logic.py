@@ -164,3 +164,14 @@ def test_mulo_groups_follow_the_infinite_width_shapes():
         mulo_param_groups([torch.nn.Parameter(torch.zeros(2, 2))])
     with pytest.raises(NotImplementedError):
         mulo_param_groups([param((2, 2, 2), 3, 1.0)])
+
+
+def test_a_rank_without_tensors_still_gets_a_param_group():
+    """The sharded drivers hang collectives on the optimizer's per-group hook; a rank that owns nothing must keep
+    (empty) groups so that the hook still runs there."""
+    from pylo_b200.zero import split_in_groups
+
+    assert split_in_groups([], 4) == [{"params": []}]
+    ps = [torch.zeros(4), torch.zeros(8), torch.zeros(4)]
+    groups = split_in_groups(ps, 2)
+    assert [len(g["params"]) for g in groups] == [2, 1]
