@@ -307,10 +307,14 @@ class FusedShardedStep(_GradIntake):
         self._group_ranges = []
         for g in out:  # a group's tensors are consecutive in the owner's region: one contiguous range
             idx = [index_of[id(p)] for p in g["params"]]
-            self._group_ranges.append((min(self.offsets[i] for i in idx), max(self.offsets[i] + self.params[i].numel() for i in idx)))
+            self._group_ranges.append((min(self.offsets[i] for i in idx), max(self.offsets[i] + self.params[i].numel() for i in idx))
+                                      if idx else (0, 0))
         return out
 
     def _push_range(self, a: int, b: int):
+        self._pushed = True
+        if b <= a:
+            return
         ev = torch.cuda.Event()
         ev.record()
         src = self.flat[a:b]
