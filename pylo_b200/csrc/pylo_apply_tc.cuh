@@ -156,6 +156,31 @@ __device__ __forceinline__ float4 ldg4_early(const float* p) {
 #endif
 
 __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
+// minus the TF32 high part of x: mask and sign flip are one three-input logic operation
+__device__ __forceinline__ float tf32_hi_neg(float x) { return __uint_as_float((__float_as_uint(x) & 0xffffe000u) ^ 0x80000000u); }
+// Split of 16 values for operand A.  hi: what goes into the high-part columns, lo: the low parts.
+// The tensor core reads only the upper 19 bits of a TF32 operand (it truncates; the parity tests against the fp32
+// kernel and the oracle would fail at the 1e-4 level if it rounded), so the high-part columns hold the unmasked
+// value and the low parts are x + (-(x & mask)), two at a time with one packed add: 2.5 instructions per pair less
+// than masking and subtracting (measured: 21.65 -> 20.65 ps per element).  -DTC_MASKED_HI builds the explicit form.
+__device__ __forceinline__ void tc_split16(const float (&x)[16], uint32_t (&hi)[16], uint32_t (&lo)[16]) {
+#ifndef TC_MASKED_HI
+#pragma unroll
+  for (int k = 0; k < 16; k += 2) {
+    float l0, l1;
+    unpack2(add2(pack2(x[k], x[k + 1]), pack2(tf32_hi_neg(x[k]), tf32_hi_neg(x[k + 1]))), l0, l1);
+    hi[k] = __float_as_uint(x[k]); hi[k + 1] = __float_as_uint(x[k + 1]);
+    lo[k] = __float_as_uint(l0); lo[k + 1] = __float_as_uint(l1);
+  }
+#else
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    const float h = tf32_hi(x[k]);
+    hi[k] = __float_as_uint(h);
+    lo[k] = __float_as_uint(x[k] - h);
+  }
+#endif
+}
 
 // One warpgroup's private shared memory: its copy of the weights and its tensor-core barrier.  Warpgroups never
 // wait on one another.
@@ -312,12 +337,7 @@ __global__ void __launch_bounds__(TC_BOUND_THREADS, 1) k_apply_adafac_tc(const p
         const float fe[16] = {g, cp, cm0, cm1, cm2, cv, cm0 * rs, cm1 * rs, cm2 * rs, rs,
                               k0 * g, k1 * g, k2 * g, k0 * cm0, k1 * cm1, k2 * cm2};
         uint32_t hi[16], lo[16];
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          const float h = tf32_hi(fe[k]);
-          hi[k] = __float_as_uint(h);
-          lo[k] = __float_as_uint(fe[k] - h);
-        }
+        tc_split16(fe, hi, lo);
         TC_CLK(10)  // features and split
         tc_st16(tA, hi);
         tc_st8(tA + 16, chi);
@@ -362,12 +382,10 @@ __global__ void __launch_bounds__(TC_BOUND_THREADS, 1) k_apply_adafac_tc(const p
         TC_CLK(3)  // accumulator read-back
         auto split_store = [&](const uint32_t (&a)[16], int half) {
           uint32_t hi[16], lo[16];
+          float v[16];
 #pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            const float v = fmaxf(__uint_as_float(a[k]), 0.f), h = tf32_hi(v);
-            hi[k] = __float_as_uint(h);
-            lo[k] = __float_as_uint(v - h);
-          }
+          for (int k = 0; k < 16; ++k) v[k] = fmaxf(__uint_as_float(a[k]), 0.f);
+          tc_split16(v, hi, lo);
           tc_st16(tA + 16 * half, hi);
           tc_st16(tA + 32 + 16 * half, lo);
         };
