@@ -136,7 +136,7 @@ def _load():
 lib, EXPORTED = _load()
 
 
-TC_WORKERS = 148 * 5  # warpgroups the tensor-core apply kernel runs at once (five per SM)
+TC_WORKERS = 148 * 4  # warpgroups the tensor-core apply kernel runs at once (four per SM)
 STATIC_SCRATCH_TILES = 65536
 ERR_STATIC_SCRATCH_TOO_SMALL = -4
 

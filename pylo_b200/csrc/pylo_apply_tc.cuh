@@ -18,10 +18,10 @@
 //   * the second-layer bias is one more product, of a constant operand A (ones, in shared memory) with a block of
 //     operand B that holds the bias's high and low parts;
 //   * relu, the split of the hidden activations, the two output heads and the parameter update stay on the CUDA
-//     cores, which work on one warpgroup's tile while the tensor core works on another's: five warpgroups per
-//     CTA, one CTA per SM; every warpgroup is an independent worker with its own work items, its own copy of the
-//     weights in shared memory, its own 96 tensor-memory columns (32 operand A high parts, 32 low parts, 32
-//     accumulator) and its own barriers, so the warpgroups drift apart instead of marching in step;
+//     cores, which work on one warpgroup's tile while the tensor core works on another's: four warpgroups per
+//     CTA (five fit), one CTA per SM; every warpgroup is an independent worker with its own work items, its own
+//     copy of the weights in shared memory, its own 96 tensor-memory columns (32 operand A high parts, 32 low
+//     parts, 32 accumulator) and its own barriers, so the warpgroups drift apart instead of marching in step;
 //   * the products are issued by one elected lane inside a warp-uniform branch (the warp index is a broadcast
 //     from lane 0), so that their descriptors and tensor-memory addresses live in uniform registers: issued from
 //     a branch on the thread index, each product cost its thread ~52 cycles; this way ~24.
@@ -31,7 +31,10 @@
 #pragma once
 
 #ifndef TC_WGS
-#define TC_WGS 5                 // warpgroups per CTA: 5 x 96 of the SM's 512 tensor-memory columns
+// Warpgroups per CTA (each uses 96 of the SM's 512 tensor-memory columns, so at most five).  Five are 8 % faster than
+// four on a short run at the full clock (20.7 against 22.4 ps per element), but the full-size step runs at the GPU's
+// power limit, where four win (246.7 against 250.3 ms per step, three: 262.4): four is the default.
+#define TC_WGS 4
 #endif
 #define TC_NT (TC_WGS * 128)
 #ifndef TC_BOUND_THREADS
