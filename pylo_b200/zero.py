@@ -379,7 +379,7 @@ class StagedShardedStep(_GradIntake):
             self.params.append(torch.nn.Parameter(view, requires_grad=True))
         self.owned = [i for i, r in enumerate(self.owner) if r == self.rank]
         self.shard = sum(self.subs)
-        self._comm = torch.cuda.Stream(device=device) if self.world > 1 else None
+        self._comm = torch.cuda.Stream(device=device) if self.world > 1 and torch.device(device).type == "cuda" else None
         self._works = []
 
     def _grad_segments(self):
@@ -414,11 +414,14 @@ class StagedShardedStep(_GradIntake):
         b, closes = self._group_info[gi]
         if not closes:
             return
-        ev = torch.cuda.Event()
-        ev.record()
         sub = self.subs[b]
         block = self.flat[self.base[b]:self.base[b] + self.world * sub]
         mine = block[self.rank * sub:(self.rank + 1) * sub]
+        if self._comm is None:   # host tensors (the gloo tests of the layout and of the order of the gathers)
+            self._works.append(dist.all_gather_into_tensor(block, mine, group=self.pg, async_op=True))
+            return
+        ev = torch.cuda.Event()
+        ev.record()
         with torch.cuda.stream(self._comm):
             self._comm.wait_event(ev)
             self._works.append(dist.all_gather_into_tensor(block, mine, group=self.pg, async_op=True))

@@ -1,5 +1,6 @@
 """The sharded step's host logic on two CPU ranks (gloo): ownership, flat views, gather."""
 
+import datetime
 import os
 import socket
 
@@ -97,6 +98,52 @@ def _worker_staged(rank, world, port, out):
         out.put((rank, traceback.format_exc()[-600:]))
     finally:
         dist.destroy_process_group()
+
+
+def _worker_idle_rank(rank, world, port, out):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        from pylo_b200 import zero
+
+        # one tensor, two ranks, three blocks: the second rank owns nothing, yet has to start every block's gather
+        shapes = [(72, 48)]
+        shard = zero.StagedShardedStep(shapes, "cpu", blocks=3, init_scale=0.05, seed=4)
+        groups = shard.param_groups()
+        counts = [None] * world
+        dist.all_gather_object(counts, (len(groups), [closes for _, closes in shard._group_info]))
+        assert counts[0] == counts[1], f"ranks disagree on their param groups: {counts}"
+        assert len(groups) == 3 and (rank == 0 or all(len(g["params"]) == 0 for g in groups))
+        before = shard.flat.clone()
+        # what an optimizer does: update the tensors of a group (if any), then call the hook - for EVERY group
+        for gi, g in enumerate(groups):
+            for p in g["params"]:
+                p.data.add_(1.0)
+            shard.after_group(gi)
+        shard.finish()
+        flats = [torch.empty_like(shard.flat) for _ in range(world)]
+        dist.all_gather(flats, shard.flat)
+        assert torch.equal(flats[0], flats[1]), "the ranks' parameter buffers differ after the gathers"
+        assert torch.equal(shard.params[0].detach(), before[shard.offsets[0]:shard.offsets[0] + 72 * 48].view(72, 48) + 1.0)
+        out.put((rank, "ok"))
+    except Exception:  # pragma: no cover
+        import traceback
+        out.put((rank, traceback.format_exc()[-600:]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_rank_without_tensors_starts_every_gather_on_two_gloo_ranks():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_idle_rank, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results
 
 
 def test_staged_layout_gradient_intake_on_two_gloo_ranks():
